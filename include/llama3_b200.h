@@ -127,6 +127,60 @@ int l3_generate_next(L3Model* m, int64_t* out_B);
 int l3_generate_ragged(L3Model* m, const int32_t* ids, const int32_t* lens, int B, int Lmax, int max_new_tokens,
                        int pos_offset, int eos_id, int64_t* out);
 
+
+/* -- layer-list decoders (hybrid stacks) ---------------------------------------------------------------
+ * A second way to make a model, for decoders that are a LIST of layers, each with its own token mixer
+ * (no counterpart in the reference, which has the one Llama block, llama3.py:238-262).  A handle made by
+ * l3_create_stack goes through the same calls as a Llama handle: l3_load_tensor (instead of l3_load_weight),
+ * l3_fill_random, l3_finalize, l3_forward / l3_forward_dev / l3_forward_rows, the l3_generate_* loop
+ * (always at contiguous positions L + i - 1), l3_reset_cache, l3_destroy and the measurement helpers.
+ * Every sequence slot b < max_batch_size owns a KV-cache region per attention layer and a recurrent state
+ * (fp32 matrix per head, plus the short convolution's tail) per recurrent layer.  A call at start_pos 0
+ * starts slot b afresh (its recurrent state is zeroed); a call at start_pos > 0 must continue exactly where
+ * the slot's previous call ended (L3_ESTATE otherwise: a recurrent state cannot be rewound). */
+#define L3_MIX_SOFTMAX 0       /* causal softmax attention, GQA, no positions, values = un-normalised keys,
+                                  RMS norm over the whole q / k projection, sigmoid gate per head            */
+#define L3_MIX_DECAY_LINEAR 1  /* linear attention, one fixed decay per head: S <- decay S + k v^T, o = S^T q */
+#define L3_MIX_GATED_DELTA 2   /* gated delta rule, one data-dependent decay per head and key channel,
+                                  short causal convolutions on q, k, v                                       */
+typedef struct L3LayerSpec {
+  int32_t mixer;        /* L3_MIX_* */
+  int32_t heads;        /* value heads (query heads for L3_MIX_SOFTMAX) */
+  int32_t kv_heads;     /* key heads (L3_MIX_DECAY_LINEAR: = heads) */
+  int32_t dim;          /* per-head query / key size */
+  int32_t vdim;         /* per-head value size */
+  int32_t conv_taps;    /* L3_MIX_GATED_DELTA: taps of the short convolutions */
+  int32_t rank_decay;   /* L3_MIX_GATED_DELTA: inner width of the two-matrix decay projection */
+  int32_t rank_gate;    /* L3_MIX_GATED_DELTA: inner width of the two-matrix output-gate projection */
+  int32_t ff;           /* width of the gated feed-forward; 0 = the layer has none */
+  float scale;          /* L3_MIX_SOFTMAX: multiplier of q . k */
+  const float* decay;   /* L3_MIX_DECAY_LINEAR: [heads] decays (host memory, copied by l3_create_stack) */
+} L3LayerSpec;
+
+typedef struct L3StackConfig {
+  int32_t width, vocab, n_layers;
+  int32_t max_seq_len, max_batch_size;
+  int32_t dtype, device, flags;   /* as in L3Config */
+  float norm_eps;
+  float residual_mult;   /* x <- x + residual_mult * norm(sublayer(x)): the norm sits on the sublayer's OUTPUT */
+  int32_t norm_one_plus; /* 1: the layer norms and the final norm multiply by (1 + w) */
+  int32_t glu_act;       /* activation of the feed-forward's gate: 0 silu, 1 tanh-GELU */
+  int32_t side_dim;      /* per-layer token input: width of each layer's slice of the side embedding; 0 = none */
+} L3StackConfig;
+
+int l3_create_stack(const L3StackConfig* cfg, const L3LayerSpec* layers, L3Model** out);
+/* One tensor by its checkpoint name ("embed", "side.embed", "l<i>.norm1", "l<i>.mix.q", "l<i>.mlp.gate",
+ * "l<i>.side.proj", "final.norm", "head", ...): float32, C-contiguous, matrices stored [out, in]. */
+int l3_load_tensor(L3Model* m, const char* name, const float* host, const int64_t* shape, int ndim);
+/* l3_forward with the logits of chosen rows: rows[i] = b * L + t of the [B, L] block, logits_out
+ * [n_rows, vocab] float32.  resid_out (may be NULL, stack handles only): the residual stream after every
+ * layer, [n_layers, B * L, width] float32.  Works for Llama handles too (resid_out must be NULL). */
+int l3_forward_rows(L3Model* m, const int32_t* ids, int B, int L, int start_pos, const int32_t* rows, int n_rows,
+                    float* logits_out, float* resid_out);
+/* Recurrent state of one layer and slot (tests): S [heads, dim, vdim] float32; conv_out (may be NULL)
+ * [channels, taps - 1] float32, the convolution's tail, oldest input first. */
+int l3_read_state(L3Model* m, int layer, int slot, float* S_out, float* conv_out);
+
 /* -- state inspection (tests): the layer's caches in the reference's layout
  * [max_batch, max_seq_len, n_kv_heads, head_dim] (llama3.py:138-153), as float32. */
 int l3_read_cache(L3Model* m, int layer, float* k_out, float* v_out);

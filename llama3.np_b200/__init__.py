@@ -16,6 +16,15 @@ def __getattr__(name):  # lazy: importing the package must not require the built
     if name in ("Llama", "compute_cos_sin_cache"):
         from . import llama3 as _l
         return getattr(_l, name)
+    if name == "Risalix":
+        from .risalix import Risalix
+        return Risalix
+    if name in ("StackDecoder", "StackConfig", "LayerSpec"):
+        from . import stack as _s
+        return getattr(_s, name)
+    if name == "load_model":
+        from .models import load_model
+        return load_model
     if name == "Tokenizer":
         from .tokenizer import Tokenizer
         return Tokenizer

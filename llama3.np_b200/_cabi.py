@@ -24,6 +24,23 @@ class L3Config(C.Structure):
                 ("tp_world", C.c_int32), ("flags", C.c_int32)]
 
 
+MIX_SOFTMAX, MIX_DECAY_LINEAR, MIX_GATED_DELTA = 0, 1, 2
+GLU_SILU, GLU_GELU_TANH = 0, 1
+
+
+class L3LayerSpec(C.Structure):
+    _fields_ = [("mixer", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32),
+                ("vdim", C.c_int32), ("conv_taps", C.c_int32), ("rank_decay", C.c_int32), ("rank_gate", C.c_int32),
+                ("ff", C.c_int32), ("scale", C.c_float), ("decay", C.POINTER(C.c_float))]
+
+
+class L3StackConfig(C.Structure):
+    _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("max_seq_len", C.c_int32),
+                ("max_batch_size", C.c_int32), ("dtype", C.c_int32), ("device", C.c_int32), ("flags", C.c_int32),
+                ("norm_eps", C.c_float), ("residual_mult", C.c_float), ("norm_one_plus", C.c_int32),
+                ("glu_act", C.c_int32), ("side_dim", C.c_int32)]
+
+
 _P = C.c_void_p
 _I = C.c_int
 _F32P = C.POINTER(C.c_float)
@@ -38,6 +55,10 @@ SIGNATURES = {
     "l3_device_count": (_I, [C.POINTER(_I)]),
     "l3_create": (_I, [C.POINTER(L3Config), C.POINTER(_P)]),
     "l3_load_weight": (_I, [_P, C.c_char_p, _F32P, _I64P, _I]),
+    "l3_create_stack": (_I, [C.POINTER(L3StackConfig), C.POINTER(L3LayerSpec), C.POINTER(_P)]),
+    "l3_load_tensor": (_I, [_P, C.c_char_p, _F32P, _I64P, _I]),
+    "l3_forward_rows": (_I, [_P, _I32P, _I, _I, _I, _I32P, _I, _F32P, _F32P]),
+    "l3_read_state": (_I, [_P, _I, _I, _F32P, _F32P]),
     "l3_fill_random": (_I, [_P, C.c_uint64]),
     "l3_save_packed": (_I, [_P, C.c_char_p, C.c_char_p]),
     "l3_load_packed": (_I, [_P, C.c_char_p, C.c_char_p]),

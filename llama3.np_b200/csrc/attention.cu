@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(128, 4) attn_decode_staged_kernel(AttnArgs a, 
   if (tid == 0)
     for (int i = 0; i < min(nstages, NST); ++i) request(i);
 
-  const float scale = 1.0f / sqrtf((float)HD);
+  const float scale = attn_scale(a, HD);
   float q[NREP][EPL], o[NREP][EPL], m[NREP], l[NREP];
   attn_decode_init<HD, NREP, KVT>(a, b, head0, sl, q, o, m, l);
   for (int i = 0; i < nstages; ++i) {
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a, int nrep)
   const int q0 = blockIdx.x * PF_ROWS;
   const int nq = min(PF_ROWS, a.L - q0);
   const int t_hi = start + q0 + nq;  // keys [0, t_hi) are visible to at least one query of the tile
-  const float scale = 1.0f / sqrtf((float)HD);
+  const float scale = attn_scale(a, HD);
 
   for (int i = tid; i < PF_ROWS * HD4; i += 256) {
     const int r = i / HD4, d4 = i % HD4;
@@ -561,7 +561,7 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a, int nrep)
     if (sidx < PF_ROWS * HD4) {
       const int r = sidx / HD4, d4 = sidx % HD4;
       if (r < nq) {
-        const float inv = 1.0f / st_l[r];
+        const float inv = attn_gate(a, (size_t)(b * a.L + q0 + r), head) / st_l[r];
         float4 o = acc[si];
         o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
         const size_t oi = ((size_t)(b * a.L + q0 + r) * a.HN + head) * HD + d4 * 4;

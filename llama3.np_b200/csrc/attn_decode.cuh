@@ -102,7 +102,7 @@ __device__ __forceinline__ void combine_splits(const AttnArgs& a, int b, int hea
     float osum = 0.f;
 #pragma unroll 8
     for (int s = 0; s < a.nsplit; ++s) osum = fmaf(__ldcg(po + (size_t)s * HD), cmb_w[r][s], osum);
-    const float v = osum / cmb_l[r];
+    const float v = osum / cmb_l[r] * attn_gate(a, (size_t)b, head);
     const size_t oi = ((size_t)b * a.HN + head) * HD + d;
     if (a.out_lo) { float hi, lo; split_tf32(v, hi, lo); __stcg(a.out + oi, hi); __stcg(a.out_lo + oi, lo); }
     else if (a.out) __stcg(a.out + oi, v);
@@ -195,7 +195,7 @@ __device__ __forceinline__ void attn_decode_finish_smem(const AttnArgs& a, int s
     }
     const int head = head0 + r;
     if (a.nsplit == 1) {
-      const float v = osum / lsum;
+      const float v = osum / lsum * attn_gate(a, (size_t)b, head);
       const size_t oi = ((size_t)b * a.HN + head) * HD + d;
       if (a.out_lo) { float hi, lo; split_tf32(v, hi, lo); __stcg(a.out + oi, hi); __stcg(a.out_lo + oi, lo); }
       else if (a.out) __stcg(a.out + oi, v);
@@ -279,7 +279,7 @@ __device__ __forceinline__ void attn_decode_item(const AttnArgs& a, int nrep_act
   const int t1 = min(T, t0 + chunk);
   const int lane = tid & 31, warp = tid >> 5;
   const int sub = lane / LPK, sl = lane % LPK;
-  const float scale = 1.0f / sqrtf((float)HD);
+  const float scale = attn_scale(a, HD);
 
   float q[NREP][EPL], o[NREP][EPL], m[NREP], l[NREP];
   attn_decode_init<HD, NREP, KVT>(a, b, head0, sl, q, o, m, l);

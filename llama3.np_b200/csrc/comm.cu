@@ -195,6 +195,7 @@ extern "C" int l3_nccl_unique_id(void* out_128) {
 extern "C" int l3_tp_init(L3Model* m, const void* nccl_unique_id_128) {
   if (!m) return L3_EINVAL;
   if (m->G == 1) return L3_OK;
+  if (m->ll) { comm_err(m, "l3_tp_init", "layer-list handles run on one GPU"); return L3_EINVAL; }
   if (m->comm) { comm_err(m, "l3_tp_init", "already initialised"); return L3_ESTATE; }
   NcclApi* n = nccl_api();
   if (!n) { comm_err(m, "libnccl.so.2 could not be loaded", "set L3_NCCL_LIB"); return L3_ENCCL; }

@@ -62,6 +62,14 @@ __device__ __forceinline__ void split_tf32(float v, float& hi, float& lo) {
 // silu exactly as the reference writes it: x * (1 / (1 + exp(-x)))   (llama3.py:27-28)
 __device__ __forceinline__ float silu_ref(float x) { return x * (1.0f / (1.0f + expf(-x))); }
 
+// tanh form of GELU: 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gelu_tanh_ref(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+// activation of a gated linear unit's gate column (EpiArgs::act)
+enum GluAct : int { GLU_SILU = 0, GLU_GELU_TANH = 1 };
+__device__ __forceinline__ float glu_act(int act, float z) { return act == GLU_GELU_TANH ? gelu_tanh_ref(z) : silu_ref(z); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(L3_FULL, v, o);
@@ -139,7 +147,7 @@ template <> struct Vec16<bf16> {
 enum Epi : int {
   EPI_STORE = 0,   // out[m, col] = v
   EPI_RESID = 1,   // out[m, col] = resid[m, col] + v          (llama3.py:253, 259)
-  EPI_SWIGLU = 2,  // out[m, col/2] = silu(v_even) * v_odd      (llama3.py:99-101; W rows interleaved gate/up)
+  EPI_SWIGLU = 2,  // out[m, col/2] = act(v_even) * v_odd       (llama3.py:99-101; W rows interleaved gate/up; act = EpiArgs::act, silu by default)
   EPI_ROPE_KV = 3, // rotate q/k pairs (llama3.py:41-76), append k, v to the cache (llama3.py:184-185)
   EPI_ARGMAX = 4   // LM head without materialised logits: best[m] = max over columns (llama3.py:320)
 };
@@ -171,6 +179,7 @@ struct EpiArgs {
                          // and leave the cache untouched (null: every token is real)
   int L;                 // tokens per sequence in this call: row m -> (b = m / L, t = m % L)
   int HD, HN, KVHN, M;   // head_dim, local heads, local kv heads, max_seq_len
+  int act;               // SWIGLU: GluAct of the gate column (0 = silu)
 };
 
 template <typename KVT>
@@ -203,7 +212,7 @@ __device__ __forceinline__ void epilogue_pair(int epi, const EpiArgs& e, int m, 
     e.out[o] = e.resid[o] + v0;
     if (has1) e.out[o + 1] = e.resid[o + 1] + v1;
   } else if (epi == EPI_SWIGLU) {
-    float h = silu_ref(v0) * v1;
+    float h = glu_act(e.act, v0) * v1;
     size_t o = (size_t)m * e.ld_out + (col >> 1);
     if (e.out_lo) {
       float hh, hl;
@@ -248,6 +257,7 @@ __device__ __forceinline__ void epilogue_pair(int epi, const EpiArgs& e, int m, 
 struct LinearArgs {
   const void* W;        // [N, K] of WT, row-major (the reference's [out, in] layout)
   const float* x;       // [*, K] fp32 activations
+  int lda;              // row stride of x in elements (0 = K); the SIMT kernels only
   int rows;             // activation rows
   int N, K;
   // optional fused RMSNorm of the input rows (llama3.py:111-114) while staging them
@@ -263,6 +273,8 @@ struct LinearArgs {
 // all launchers return cudaGetLastError() of the launch
 cudaError_t launch_linear_rows(const LinearArgs& a, bool w_bf16, bool kv_bf16, cudaStream_t s);   // GEMV family, rows <= 8
 cudaError_t launch_linear_simt(const LinearArgs& a, bool w_bf16, bool kv_bf16, cudaStream_t s);   // tiled FFMA GEMM
+// any N, K, row stride (scalar loads); epilogues STORE / RESID / SWIGLU
+cudaError_t launch_linear_any(const LinearArgs& a, bool w_bf16, cudaStream_t s);
 bool linear_rows_supported(int rows, int K);
 
 // row r = (b, t) = (r / L, r % L) reads token ids[b * ids_ld + ids_off + t]
@@ -324,7 +336,15 @@ struct AttnArgs {
   unsigned long long* out_ll;  // [B*L, HN*HD] words (null: off)
   unsigned out_tag;
   int force_exact;     // decode over a bf16 cache: never the tensor-core kernel (which rounds q and the softmax weights to bf16)
+  float scale;         // multiplier of q . k; 0 = 1 / sqrt(HD) (llama3.py:190).  Honoured by the exact kernels (set force_exact)
+  const float* head_gate;  // optional output gate: head h of row r is multiplied by sigmoid(head_gate[r * ld_gate + h])
+  int ld_gate;
 };
+// score multiplier and per-(row, head) output gate of an attention launch
+__device__ __forceinline__ float attn_scale(const AttnArgs& a, int HD) { return a.scale != 0.f ? a.scale : 1.0f / sqrtf((float)HD); }
+__device__ __forceinline__ float attn_gate(const AttnArgs& a, size_t row, int head) {
+  return a.head_gate ? 1.0f / (1.0f + expf(-a.head_gate[row * a.ld_gate + head])) : 1.0f;
+}
 cudaError_t launch_attn_decode(const AttnArgs& a, bool kv_bf16, cudaStream_t s);   // L == 1
 // whether launch_attn_decode runs the tensor-core (mma.sync) kernel for this shape once the launch has >= 96 CTAs
 bool attn_decode_mma_eligible(int HD, int nrep, bool kv_bf16);

@@ -502,7 +502,8 @@ __device__ __forceinline__ void tc_gemm_run(TcPipe& p, const CUtensorMap* tmA0p,
               if (m >= rows) break;
               const float2 t = *reinterpret_cast<const float2*>(Cs + i * LDC + cp);
               float hv;
-              if constexpr (KIND == TC_BF16) hv = t.x * __fdividef(1.0f, 1.0f + __expf(-t.x)) * t.y;
+              if (e.act != GLU_SILU) hv = glu_act(e.act, t.x) * t.y;
+              else if constexpr (KIND == TC_BF16) hv = t.x * __fdividef(1.0f, 1.0f + __expf(-t.x)) * t.y;
               else hv = silu_ref(t.x) * t.y;
               const size_t o = (size_t)m * e.ld_out + (col >> 1);
               if (e.out_lo) { float hh, hl; split_tf32(hv, hh, hl); e.out[o] = hh; e.out_lo[o] = hl; }

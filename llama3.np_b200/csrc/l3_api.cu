@@ -13,12 +13,14 @@
 #include "../../include/llama3_b200.h"
 #include "common.cuh"
 #include "gemm_tc.h"
+#include "internal.h"
+#include "layerlist.h"
 #include "mega.h"
 #include "model.h"
 #include "stack.h"
 
 static thread_local char g_err[512] = "";
-static const bool g_l3_debug_sync = getenv("L3_DEBUG_SYNC") && atoi(getenv("L3_DEBUG_SYNC")) != 0;
+const bool g_l3_debug_sync = getenv("L3_DEBUG_SYNC") && atoi(getenv("L3_DEBUG_SYNC")) != 0;
 bool g_l3_pdl_next = false;  // one-shot: the next launch is a programmatic dependent of its predecessor (linear())
 bool g_l3_pdl = false;  // programmatic dependent launch for step kernels (common.cuh); measured slower
                         // than plain graph edges on this workload, so opt-in (L3_PDL=1)
@@ -44,37 +46,6 @@ void set_err(L3Model* m, const char* fmt, ...) {  // also used by packed_io.cu
   snprintf(g_err, sizeof g_err, "%s", buf);
   if (m) snprintf(m->err, sizeof m->err, "%s", buf);
 }
-
-#define CK(m, call)                                                                         \
-  do {                                                                                      \
-    cudaError_t e__ = (call);                                                               \
-    if (e__ != cudaSuccess) {                                                               \
-      set_err(m, "CUDA error %s at %s:%d: %s", cudaGetErrorName(e__), __FILE__, __LINE__,   \
-              cudaGetErrorString(e__));                                                     \
-      return L3_ECUDA;                                                                      \
-    }                                                                                       \
-  } while (0)
-// a kernel launch: counted (gpu_launches in bench.py is this counter)
-#define LAUNCH(m, call)                                                                        \
-  do {                                                                                         \
-    CK(m, call);                                                                               \
-    (m)->launch_acc += 1;                                                                      \
-    if (g_l3_debug_sync) { /* L3_DEBUG_SYNC=1: attribute an asynchronous fault to its launch */ \
-      cudaError_t e2__ = cudaStreamSynchronize((m)->stream);                                   \
-      if (e2__ != cudaSuccess) {                                                               \
-        set_err(m, "kernel launched at %s:%d (launch #%lld) failed: %s", __FILE__, __LINE__,   \
-                (long long)(m)->launch_acc, cudaGetErrorString(e2__));                         \
-        return L3_ECUDA;                                                                       \
-      }                                                                                        \
-    }                                                                                          \
-  } while (0)
-#define REQUIRE(m, cond, ...)    \
-  do {                           \
-    if (!(cond)) {               \
-      set_err(m, __VA_ARGS__);   \
-      return L3_EINVAL;          \
-    }                            \
-  } while (0)
 
 extern "C" const char* l3_version(void) { return "llama3_b200 0.1 (sm_100a)"; }
 extern "C" const char* l3_last_error(const L3Model* m) { return m ? m->err : g_err; }
@@ -169,6 +140,7 @@ extern "C" int l3_destroy(L3Model* m) {
   }
   m->graphs.clear();
   tp_destroy(m);
+  ll_destroy(m);
   if (m->logits_loc) cudaFree(m->logits_loc);
   if (m->logits_all) cudaFree(m->logits_all);
   auto fr = [](void* p) { if (p) cudaFree(p); };
@@ -262,6 +234,7 @@ static size_t loaded_slot(const KeyInfo& ki) { return ki.layer < 0 ? (size_t)ki.
 
 extern "C" int l3_load_weight(L3Model* m, const char* key, const float* host, const int64_t* shape, int ndim) {
   if (!m) return L3_EINVAL;
+  REQUIRE(m, !m->ll, "a layer-list handle takes its tensors through l3_load_tensor");
   REQUIRE(m, !m->finalized, "l3_load_weight after l3_finalize");
   CK(m, cudaSetDevice(m->cfg.device));
   KeyInfo ki;
@@ -294,6 +267,7 @@ extern "C" int l3_fill_random(L3Model* m, uint64_t seed) {
   if (!m) return L3_EINVAL;
   REQUIRE(m, !m->finalized, "l3_fill_random after l3_finalize");
   CK(m, cudaSetDevice(m->cfg.device));
+  if (m->ll) return ll_fill_random(m, seed);
   std::vector<KeyInfo> keys = {{-1, 0}, {-1, 1}, {-1, 2}};
   for (int l = 0; l < m->cfg.n_layers; ++l)
     for (int k = K_Q; k <= K_NPOST; ++k) keys.push_back({l, k});
@@ -310,6 +284,7 @@ extern "C" int l3_fill_random(L3Model* m, uint64_t seed) {
 
 extern "C" int l3_set_rope_tables(L3Model* m, const double* cos_tab, const double* sin_tab) {
   if (!m) return L3_EINVAL;
+  REQUIRE(m, !m->ll, "layer-list handles have no rotary tables");
   CK(m, cudaSetDevice(m->cfg.device));
   const size_t n = (size_t)m->M * (m->HD / 2);
   std::vector<float> c(n), s(n);
@@ -324,6 +299,7 @@ extern "C" int l3_finalize(L3Model* m) {
   if (!m) return L3_EINVAL;
   REQUIRE(m, !m->finalized, "already finalized");
   CK(m, cudaSetDevice(m->cfg.device));
+  if (m->ll) return ll_finalize(m);
   for (size_t i = 0; i < m->loaded.size(); ++i)
     if (!m->loaded[i]) { set_err(m, "weight slot %zu was never loaded", i); return L3_ESTATE; }
   if (!m->rope_set) { set_err(m, "l3_set_rope_tables was not called"); return L3_ESTATE; }
@@ -470,6 +446,12 @@ extern "C" int l3_finalize(L3Model* m) {
 extern "C" int l3_reset_cache(L3Model* m) {
   if (!m || !m->finalized) return L3_ESTATE;
   CK(m, cudaSetDevice(m->cfg.device));
+  if (m->ll) {
+    const int rc = ll_reset_slots(m, 0, m->maxB, true);
+    if (rc != L3_OK) return rc;
+    CK(m, cudaStreamSynchronize(m->stream));
+    return L3_OK;
+  }
   const size_t cache_bytes = (size_t)m->maxB * m->KVHN * m->M * m->HD * (m->bf16 ? 2 : 4);
   for (auto& L : m->layers) {
     CK(m, cudaMemsetAsync(L.ck, 0, cache_bytes, m->stream));
@@ -483,6 +465,23 @@ extern "C" int l3_read_cache(L3Model* m, int layer, float* k_out, float* v_out) 
   if (!m || !m->finalized) return L3_ESTATE;
   REQUIRE(m, layer >= 0 && layer < m->cfg.n_layers, "layer out of range");
   CK(m, cudaSetDevice(m->cfg.device));
+  if (m->ll) {  // a softmax layer of a layer-list handle: its own head count and size
+    const LLLayer& Ly = m->ll->layers[layer];
+    REQUIRE(m, Ly.spec.mixer == L3_MIX_SOFTMAX, "layer %d keeps a recurrent state, not a KV cache (l3_read_state)", layer);
+    const int G = Ly.spec.kv_heads, HD = Ly.spec.dim;
+    const size_t n = (size_t)m->maxB * G * m->M * HD;
+    float* tmp = nullptr;
+    CK(m, cudaMalloc((void**)&tmp, n * 4));
+    for (int which = 0; which < 2; ++which) {
+      float* dst = which ? v_out : k_out;
+      if (!dst) continue;
+      CK(m, launch_cache_to_ref_layout(which ? Ly.cv : Ly.ck, m->bf16, m->maxB, G, m->M, HD, tmp, m->stream));
+      CK(m, cudaMemcpyAsync(dst, tmp, n * 4, cudaMemcpyDeviceToHost, m->stream));
+      CK(m, cudaStreamSynchronize(m->stream));
+    }
+    cudaFree(tmp);
+    return L3_OK;
+  }
   const size_t n = (size_t)m->maxB * m->KVHN * m->M * m->HD;
   float* tmp = nullptr;
   CK(m, cudaMalloc((void**)&tmp, n * 4));
@@ -622,9 +621,22 @@ static int tp_row_parallel(L3Model* m, LinearArgs& a, Feed feed, const float* w_
 }
 
 // Enqueue one chunk: tokens ids[b * ids_ld + ids_off + t], t < L, at start_pos = *d_pos.
+// Layer-list handles: d_rows / n_rows choose the rows whose logits are wanted (null: the last token of every sequence),
+// d_resid (may be null) receives the residual stream after every layer.
 static int enqueue_chunk(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off, int B, int L, bool want_logits,
-                         bool want_argmax, OutSpec os, const Ragged* rg = nullptr) {
+                         bool want_argmax, OutSpec os, const Ragged* rg = nullptr, const int32_t* d_rows = nullptr,
+                         int n_rows = 0, float* d_resid = nullptr) {
   const int ntok = B * L, D = m->D, HD = m->HD;
+  if (m->ll) {
+    LAUNCH(m, launch_embed(m->embed, m->bf16, d_ids, ids_ld, ids_off, L, ntok, D, m->cfg.vocab_size, m->x, m->stream));
+    int rc = ll_enqueue_layers(m, d_ids, ids_ld, ids_off, B, L, d_resid);
+    if (rc != L3_OK) return rc;
+    if (want_logits || want_argmax) {
+      if ((rc = ll_enqueue_head(m, B, L, d_rows, n_rows)) != L3_OK) return rc;
+      if (want_argmax) LAUNCH(m, launch_argmax(m->logits, B, m->VS, os.next, os.out64, os.stride, os.step_ptr, m->stream));
+    }
+    return L3_OK;
+  }
   int* d_pos = m->d_scal + 0;
   // do this chunk's projections run as tensor-core GEMMs?  (their producers then write operands)
   const bool tc_rows = m->tc_ok && !linear_rows_supported(ntok, D);
@@ -719,9 +731,16 @@ static int enqueue_chunk(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_o
 
 // Prefill of [B, L] at start_pos, in chunks of at most cap_tok rows.
 static int enqueue_prefill(L3Model* m, const int32_t* d_ids, int B, int L, int start_pos, bool want_logits,
-                           bool want_argmax, OutSpec os) {
+                           bool want_argmax, OutSpec os, const int32_t* d_rows = nullptr, int n_rows = 0,
+                           float* d_resid = nullptr) {
   int* d_pos = m->d_scal + 0;
+  if (m->ll) {  // a call at position 0 starts its slots afresh; any other must continue them
+    const int rc = ll_begin_call(m, B, L, start_pos);
+    if (rc != L3_OK) return rc;
+  }
   LAUNCH(m, launch_set_int(d_pos, start_pos, m->stream));
+  if (d_rows || d_resid)  // chosen rows / the residual trace index the whole block: one chunk (checked by the caller)
+    return enqueue_chunk(m, d_ids, L, 0, B, L, want_logits, want_argmax, os, nullptr, d_rows, n_rows, d_resid);
   const int lc_max = std::max(1, m->cap_tok / B);
   for (int l0 = 0; l0 < L; l0 += lc_max) {
     const int lc = std::min(lc_max, L - l0);
@@ -773,6 +792,42 @@ extern "C" int l3_forward(L3Model* m, const int32_t* ids, int B, int L, int star
   if (argmax_out)
     CK(m, cudaMemcpyAsync(argmax_out, m->d_fwd_arg, (size_t)B * 8, cudaMemcpyDeviceToHost, m->stream));
   CK(m, cudaStreamSynchronize(m->stream));
+  return L3_OK;
+}
+
+extern "C" int l3_forward_rows(L3Model* m, const int32_t* ids, int B, int L, int start_pos, const int32_t* rows, int n_rows,
+                               float* logits_out, float* resid_out) {
+  int rc = check_call(m, B, L, start_pos);
+  if (rc != L3_OK) return rc;
+  REQUIRE(m, m->ll != nullptr, "l3_forward_rows needs a handle made by l3_create_stack");
+  REQUIRE(m, n_rows >= 0 && (n_rows == 0 || (rows && logits_out)), "rows / logits_out missing");
+  REQUIRE(m, (int64_t)B * L <= m->cap_tok, "%d x %d tokens exceed one chunk of %d rows: feed the block in pieces", B, L, m->cap_tok);
+  CK(m, cudaSetDevice(m->cfg.device));
+  for (int i = 0; i < B * L; ++i)
+    REQUIRE(m, ids[i] >= 0 && ids[i] < m->cfg.vocab_size, "token id %d out of range at %d", ids[i], i);
+  for (int i = 0; i < n_rows; ++i) REQUIRE(m, rows[i] >= 0 && rows[i] < B * L, "row %d out of range", rows[i]);
+  if ((rc = ll_ensure_head_rows(m, n_rows)) != L3_OK) return rc;
+  int32_t* d_rows = nullptr;
+  float* d_resid = nullptr;
+  if (n_rows) {
+    CK(m, cudaMalloc((void**)&d_rows, (size_t)n_rows * 4));
+    CK(m, cudaMemcpyAsync(d_rows, rows, (size_t)n_rows * 4, cudaMemcpyHostToDevice, m->stream));
+  }
+  const size_t nres = (size_t)m->cfg.n_layers * B * L * m->D;
+  if (resid_out) CK(m, cudaMalloc((void**)&d_resid, nres * 4));
+  CK(m, cudaMemcpyAsync(m->d_fwd_ids, ids, (size_t)B * L * 4, cudaMemcpyHostToDevice, m->stream));
+  rc = enqueue_prefill(m, m->d_fwd_ids, B, L, start_pos, n_rows > 0, false, OutSpec{m->d_fwd_arg, 1, m->d_scal + 3, m->d_fwd_next},
+                       d_rows ? d_rows : nullptr, n_rows, d_resid);
+  cudaError_t e = cudaSuccess;
+  if (rc == L3_OK && n_rows)
+    e = cudaMemcpyAsync(logits_out, m->logits, (size_t)n_rows * m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->stream);
+  if (rc == L3_OK && e == cudaSuccess && resid_out) e = cudaMemcpyAsync(resid_out, d_resid, nres * 4, cudaMemcpyDeviceToHost, m->stream);
+  const cudaError_t e2 = cudaStreamSynchronize(m->stream);
+  if (d_rows) cudaFree(d_rows);
+  if (d_resid) cudaFree(d_resid);
+  if (rc != L3_OK) return rc;
+  CK(m, e);
+  CK(m, e2);
   return L3_OK;
 }
 
@@ -866,6 +921,8 @@ static int enqueue_decode_nodes(L3Model* m, int B, int ragged, int eos) {
 }
 
 static int decode_step(L3Model* m, int B, int ragged = 0, int eos = -1) {
+  if (m->ll)
+    for (int b = 0; b < B; ++b) m->ll->slot_pos[b] += 1;
   L3Graph* g = nullptr;
   const int key = ragged ? ragged + 4 * (eos + 1) : 0;  // the EOS id is baked into the captured node
   for (auto& it : m->graphs)
@@ -915,7 +972,7 @@ extern "C" int l3_generate_greedy_dev(L3Model* m, const int32_t* d_ids, int B, i
   const int n_out = max_new_tokens - L;
   if (n_out <= 0) return L3_OK;
   CK(m, cudaSetDevice(m->cfg.device));
-  m->gen_off = 0;
+  m->gen_off = m->ll ? -1 : 0;  // layer-list decoders generate at contiguous positions
   if ((rc = generate_begin_dev(m, d_ids, B, L)) != L3_OK) return rc;
   for (int i = 1; i < n_out; ++i)
     if ((rc = decode_step(m, B)) != L3_OK) return rc;
@@ -934,7 +991,7 @@ extern "C" int l3_generate_greedy(L3Model* m, const int32_t* ids, int B, int L, 
   for (int i = 0; i < B * L; ++i)
     REQUIRE(m, ids[i] >= 0 && ids[i] < m->cfg.vocab_size, "token id %d out of range at %d", ids[i], i);
   CK(m, cudaMemcpyAsync(m->d_ids, ids, (size_t)B * L * 4, cudaMemcpyHostToDevice, m->stream));
-  m->gen_off = 0;
+  m->gen_off = m->ll ? -1 : 0;  // layer-list decoders generate at contiguous positions
   if ((rc = generate_begin_dev(m, m->d_ids, B, L)) != L3_OK) return rc;
   for (int i = 1; i < n_out; ++i)
     if ((rc = decode_step(m, B)) != L3_OK) return rc;
@@ -954,6 +1011,7 @@ extern "C" int l3_generate_ragged(L3Model* m, const int32_t* ids, const int32_t*
   int rc = check_call(m, B, Lmax, 0);
   if (rc != L3_OK) return rc;
   REQUIRE(m, pos_offset == 0 || pos_offset == -1, "pos_offset must be 0 (llama3.py) or -1 (llama3_simple.py)");
+  REQUIRE(m, !m->ll, "ragged batches are not built for layer-list handles");
   REQUIRE(m, B <= 1024, "at most 1024 sequences per ragged batch");
   REQUIRE(m, (int64_t)B * Lmax <= m->cap_tok, "ragged prompts must fit one chunk: %d x %d > %d rows", B, Lmax, m->cap_tok);
   REQUIRE(m, max_new_tokens >= 1, "max_new_tokens must be >= 1");
@@ -997,7 +1055,7 @@ extern "C" int l3_generate_begin_ex(L3Model* m, const int32_t* ids, int B, int L
   int rc = check_call(m, B, L, 0);
   if (rc != L3_OK) return rc;
   REQUIRE(m, pos_offset == 0 || pos_offset == -1, "pos_offset must be 0 (llama3.py) or -1 (llama3_simple.py)");
-  m->pend_off = pos_offset;
+  m->pend_off = m->ll ? -1 : pos_offset;
   CK(m, cudaSetDevice(m->cfg.device));
   for (int i = 0; i < B * L; ++i)
     REQUIRE(m, ids[i] >= 0 && ids[i] < m->cfg.vocab_size, "token id %d out of range at %d", ids[i], i);
@@ -1118,6 +1176,7 @@ extern "C" int l3_launch_count(L3Model* m, int64_t* out, int reset) {
 extern "C" int l3_bench_kernel(L3Model* m, int which, int B, int pos, int iters, float* avg_ms) {
   int rc = check_call(m, B, 1, pos);
   if (rc != L3_OK) return rc;
+  REQUIRE(m, !m->ll, "l3_bench_kernel times kernels of the Llama path");
   CK(m, cudaSetDevice(m->cfg.device));
   REQUIRE(m, iters >= 1, "iters must be >= 1");
   int* d_pos = m->d_scal + 0;

@@ -1,0 +1,596 @@
+// Layer-list decoders: creation, tensors by checkpoint name, per-slot state, and the layers of one step.
+//
+// A layer is  x += m N1(mixer(x));  x += m N2(ff(x)) [if it has one];  x += m Ns(token_input(x)) [if side_dim]
+// with the norm on the sublayer's OUTPUT (N = RMS norm, weight w or 1 + w), the residual stream x in fp32.
+// Three mixers (include/llama3_b200.h, L3_MIX_*), each a chain of launches that share the projection kernels of
+// the Llama path (row-streaming GEMV for <= 8 rows, tcgen05 GEMMs in bf16 mode, FFMA GEMMs in fp32 mode):
+//
+//   softmax       fused q|k|gate projection -> whole-projection q / k norm + KV append (values = raw keys)
+//                 -> causal attention with the score multiplier and the per-head sigmoid gate in its epilogue
+//   decay-linear  fused q|k|v|gate projection -> recurrence (recurrent.cu, silu on load) -> row norm * gate
+//   gated delta   fused q|k|v|beta|a1|g1 projection -> a2, g2 -> convolutions, unit vectors, decays
+//                 (delta_prep_kernel) -> recurrence -> per-head norm * gate
+//   then the output projection and the post-norm residual kernel, which also emits the bf16 mirror of the new
+//   residual rows for the next tensor-core projection.
+//
+// Precision: norms, gates, decays, scores, softmax, recurrent state and the residual sum are fp32 in both
+// modes; bf16 mode rounds only GEMM operands (weights, and activations on the tensor-core path) and the KV cache.
+#include "layerlist.h"
+
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "gemm_tc.h"
+#include "internal.h"
+#include "mixer.h"
+
+static size_t wb(const L3Model* m) { return m->bf16 ? 2 : 4; }
+static int pad8(int v) { return (v + 7) & ~7; }
+
+// ------------------------------------------------------------------------------ create
+static int check_spec(const L3StackConfig* c, const L3LayerSpec& s, int i) {
+  REQUIRE(nullptr, s.mixer >= L3_MIX_SOFTMAX && s.mixer <= L3_MIX_GATED_DELTA, "layer %d: unknown mixer %d", i, s.mixer);
+  REQUIRE(nullptr, s.heads >= 1 && s.dim >= 1 && s.vdim >= 1 && s.ff >= 0, "layer %d: bad sizes", i);
+  if (s.mixer == L3_MIX_SOFTMAX) {
+    REQUIRE(nullptr, s.kv_heads >= 1 && s.heads % s.kv_heads == 0, "layer %d: heads %% kv_heads != 0", i);
+    REQUIRE(nullptr, s.vdim == s.dim, "layer %d: the values of this attention are its keys, so vdim must equal dim", i);
+  } else if (s.mixer == L3_MIX_DECAY_LINEAR) {
+    REQUIRE(nullptr, s.decay != nullptr, "layer %d: decay-linear mixer without decays", i);
+    REQUIRE(nullptr, recur_supported(s.dim, s.vdim), "layer %d: state %d x %d unsupported", i, s.dim, s.vdim);
+  } else {
+    REQUIRE(nullptr, s.kv_heads >= 1 && s.heads % s.kv_heads == 0, "layer %d: heads %% kv_heads != 0", i);
+    REQUIRE(nullptr, s.conv_taps >= 1 && s.conv_taps <= 64 && s.rank_decay >= 1 && s.rank_gate >= 1, "layer %d: bad conv / rank sizes", i);
+    REQUIRE(nullptr, recur_supported(s.dim, s.vdim), "layer %d: state %d x %d unsupported", i, s.dim, s.vdim);
+  }
+  (void)c;
+  return L3_OK;
+}
+
+extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs, L3Model** out) {
+  *out = nullptr;
+  REQUIRE(nullptr, c && specs && c->width >= 1 && c->vocab >= 1 && c->n_layers >= 1, "bad stack config");
+  REQUIRE(nullptr, c->max_batch_size >= 1 && c->max_seq_len >= 1, "bad sizes");
+  REQUIRE(nullptr, c->dtype == L3_DTYPE_F32 || c->dtype == L3_DTYPE_BF16, "bad dtype");
+  REQUIRE(nullptr, c->side_dim >= 0 && (c->glu_act == GLU_SILU || c->glu_act == GLU_GELU_TANH), "bad side_dim / glu_act");
+  for (int i = 0; i < c->n_layers; ++i) {
+    const int rc = check_spec(c, specs[i], i);
+    if (rc != L3_OK) return rc;
+  }
+  L3Model* m = new L3Model();
+  LayerList* ll = m->ll = new LayerList();
+  ll->cfg = *c;
+  m->cfg.dim = c->width; m->cfg.n_layers = c->n_layers; m->cfg.n_heads = 1; m->cfg.n_kv_heads = 1;
+  m->cfg.vocab_size = c->vocab; m->cfg.max_seq_len = c->max_seq_len; m->cfg.max_batch_size = c->max_batch_size;
+  m->cfg.hidden_dim = 0; m->cfg.norm_eps = c->norm_eps; m->cfg.dtype = c->dtype; m->cfg.device = c->device;
+  m->cfg.tp_rank = 0; m->cfg.tp_world = 1; m->cfg.flags = c->flags;
+  m->bf16 = c->dtype == L3_DTYPE_BF16;
+  m->D = c->width; m->HD = 0; m->G = 1; m->HN = 0; m->KVHN = 0; m->FD = 0; m->VS = c->vocab; m->M = c->max_seq_len;
+  m->maxB = c->max_batch_size;
+  if (cudaSetDevice(c->device) != cudaSuccess) {
+    set_err(nullptr, "cudaSetDevice(%d) failed: %s", c->device, cudaGetErrorString(cudaGetLastError()));
+    delete ll; delete m;
+    return L3_ECUDA;
+  }
+  cudaError_t e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) { set_err(nullptr, "stream: %s", cudaGetErrorString(e)); delete ll; delete m; return L3_ECUDA; }
+  cudaEventCreate(&m->ev0);
+  cudaEventCreate(&m->ev1);
+  const size_t w = wb(m);
+  const int W = c->width, sd = c->side_dim;
+#define AL(p, bytes)                                                                          \
+  if ((e = cudaMalloc((void**)&(p), std::max<size_t>(16, (bytes)))) != cudaSuccess) {          \
+    set_err(nullptr, "cudaMalloc(%zu) failed: %s", (size_t)(bytes), cudaGetErrorString(e));   \
+    l3_destroy(m);                                                                            \
+    return L3_ENOMEM;                                                                         \
+  }
+  AL(m->embed, (size_t)c->vocab * W * w);
+  AL(m->lm_head, (size_t)c->vocab * W * w);
+  AL(m->norm_final, (size_t)W * 4);
+  if (sd) AL(ll->side_embed, (size_t)c->vocab * c->n_layers * sd * w);
+  ll->layers.resize(c->n_layers);
+  for (int i = 0; i < c->n_layers; ++i) {
+    LLLayer& L = ll->layers[i];
+    L.spec = specs[i];
+    const L3LayerSpec& s = L.spec;
+    const int H = s.heads, G = s.mixer == L3_MIX_DECAY_LINEAR ? s.heads : s.kv_heads, DK = s.dim, DV = s.vdim;
+    L.spec.kv_heads = G;
+    if (s.mixer == L3_MIX_SOFTMAX) {
+      L.off_q = 0; L.off_k = H * DK; L.off_g = L.off_k + G * DK; L.n_in = L.off_g + H;
+      AL(L.q_norm, (size_t)H * DK * 4);
+      AL(L.k_norm, (size_t)G * DK * 4);
+    } else if (s.mixer == L3_MIX_DECAY_LINEAR) {
+      L.off_q = 0; L.off_k = H * DK; L.off_v = 2 * H * DK; L.off_g = L.off_v + H * DV; L.n_in = L.off_g + H * DV;
+      AL(L.mix_norm, (size_t)H * DV * 4);
+      AL(L.decay, (size_t)H * 4);
+      if ((e = cudaMemcpy(L.decay, s.decay, (size_t)H * 4, cudaMemcpyHostToDevice)) != cudaSuccess) {
+        set_err(nullptr, "decay upload: %s", cudaGetErrorString(e)); l3_destroy(m); return L3_ECUDA;
+      }
+      L.spec.decay = nullptr;  // the caller's array is not kept
+    } else {
+      // q | k | v stay contiguous (a convolution channel is a column); the inner projections start on a
+      // multiple of 8 columns so that the second-stage projections read 16-byte aligned rows
+      L.off_q = 0; L.off_k = G * DK; L.off_v = 2 * G * DK; L.off_b = L.off_v + H * DV;
+      L.off_a1 = pad8(L.off_b + H); L.off_g1 = pad8(L.off_a1 + s.rank_decay); L.n_in = pad8(L.off_g1 + s.rank_gate);
+      AL(L.mix_norm, (size_t)DV * 4);
+      AL(L.w_a2, (size_t)H * DK * s.rank_decay * w);
+      AL(L.w_g2, (size_t)H * DV * s.rank_gate * w);
+      AL(L.conv_w, (size_t)(2 * G * DK + H * DV) * s.conv_taps * 4);
+      AL(L.A_log, (size_t)H * 4);
+      AL(L.dt_bias, (size_t)H * DK * 4);
+    }
+    AL(L.w_in, (size_t)L.n_in * W * w);
+    cudaMemset(L.w_in, 0, (size_t)L.n_in * W * w);  // padding rows project to zero
+    AL(L.w_o, (size_t)W * H * DV * w);
+    AL(L.norm1, (size_t)W * 4);
+    if (s.ff > 0) {
+      AL(L.w13, (size_t)2 * s.ff * W * w);
+      AL(L.w2, (size_t)W * s.ff * w);
+      AL(L.norm2, (size_t)W * 4);
+    }
+    if (sd) {
+      AL(L.side_gate, (size_t)sd * W * w);
+      AL(L.side_proj, (size_t)W * sd * w);
+      AL(L.side_norm, (size_t)W * 4);
+    }
+    ll->max_in = std::max(ll->max_in, L.n_in);
+    ll->max_o = std::max(ll->max_o, std::max(H * DV, H * DK));
+    ll->max_ff = std::max(ll->max_ff, s.ff);
+  }
+#undef AL
+  ll->slot_pos.assign(c->max_batch_size, 0);
+  *out = m;
+  return L3_OK;
+}
+
+// ------------------------------------------------------------------------------ tensors by name
+// Where a named tensor lives: destination, its logical shape, and the row mapping inside a fused matrix.
+struct LLPlace {
+  void* dst = nullptr;
+  bool wt = true;        // stored in the model dtype (false: fp32 vector / table)
+  int64_t rows = 0, cols = 1;
+  int row0 = 0, row_stride = 1, ld = 1;
+  bool one_plus = false; // stored as 1 + w
+  float scale = 0.f, bias = 0.f;  // random init
+};
+
+static bool ll_place(L3Model* m, const std::string& name, LLPlace* p) {
+  LayerList* ll = m->ll;
+  const int W = ll->cfg.width, V = ll->cfg.vocab, sd = ll->cfg.side_dim, NL = ll->cfg.n_layers;
+  const bool op = ll->cfg.norm_one_plus != 0;
+  *p = LLPlace{};
+  auto mat = [&](void* d, int64_t r, int64_t c, int row0 = 0, int stride = 1) {
+    p->dst = d; p->wt = true; p->rows = r; p->cols = c; p->row0 = row0; p->row_stride = stride; p->ld = (int)c;
+    p->scale = 1.0f / sqrtf((float)c);
+    return d != nullptr;
+  };
+  auto vec = [&](float* d, int64_t n, float bias, float scale, bool one_plus = false) {
+    p->dst = d; p->wt = false; p->rows = n; p->cols = 1; p->ld = 1; p->bias = bias; p->scale = scale; p->one_plus = one_plus;
+    return d != nullptr;
+  };
+  if (name == "embed") { const bool ok = mat(m->embed, V, W); p->scale = 1.0f; return ok; }
+  if (name == "head") return mat(m->lm_head, V, W);
+  if (name == "final.norm") return vec(m->norm_final, W, op ? 0.f : 1.f, 0.1f, op);
+  if (name == "side.embed") { const bool ok = sd && mat(ll->side_embed, V, (int64_t)NL * sd); p->scale = 1.0f; return ok; }
+  int li = -1, n = 0;
+  if (sscanf(name.c_str(), "l%d.%n", &li, &n) < 1 || n == 0 || li < 0 || li >= NL) return false;
+  const std::string r = name.substr(n);
+  LLLayer& L = ll->layers[li];
+  const L3LayerSpec& s = L.spec;
+  const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
+  if (r == "norm1") return vec(L.norm1, W, op ? 0.f : 1.f, 0.1f, op);
+  if (r == "norm2") return s.ff > 0 && vec(L.norm2, W, op ? 0.f : 1.f, 0.1f, op);
+  if (r == "mlp.gate") return s.ff > 0 && mat(L.w13, s.ff, W, 0, 2);
+  if (r == "mlp.up") return s.ff > 0 && mat(L.w13, s.ff, W, 1, 2);
+  if (r == "mlp.down") return s.ff > 0 && mat(L.w2, W, s.ff);
+  if (r == "side.gate") return sd && mat(L.side_gate, sd, W);
+  if (r == "side.proj") return sd && mat(L.side_proj, W, sd);
+  if (r == "side.norm") return sd && vec(L.side_norm, W, 1.f, 0.1f);
+  if (r == "mix.o") return mat(L.w_o, W, (int64_t)H * DV);
+  auto seg = [&](int off, int64_t rows) { const bool ok = mat(L.w_in, rows, W, off, 1); return ok; };
+  if (s.mixer == L3_MIX_SOFTMAX) {
+    if (r == "mix.q") return seg(L.off_q, (int64_t)H * DK);
+    if (r == "mix.k") return seg(L.off_k, (int64_t)G * DK);
+    if (r == "mix.g") return seg(L.off_g, H);
+    if (r == "mix.q.norm") return vec(L.q_norm, (int64_t)H * DK, 1.f, 0.1f);
+    if (r == "mix.k.norm") return vec(L.k_norm, (int64_t)G * DK, 1.f, 0.1f);
+    return false;
+  }
+  if (s.mixer == L3_MIX_DECAY_LINEAR) {
+    if (r == "mix.q") { const bool ok = seg(L.off_q, (int64_t)H * DK); p->scale *= 2.f; return ok; }
+    if (r == "mix.k") { const bool ok = seg(L.off_k, (int64_t)H * DK); p->scale *= 2.f; return ok; }
+    if (r == "mix.v") { const bool ok = seg(L.off_v, (int64_t)H * DV); p->scale *= 2.f; return ok; }
+    if (r == "mix.g") return seg(L.off_g, (int64_t)H * DV);
+    if (r == "mix.norm") return vec(L.mix_norm, (int64_t)H * DV, 1.f, 0.1f);
+    return false;
+  }
+  const int nq = G * DK, nv = H * DV;
+  if (r == "mix.q") { const bool ok = seg(L.off_q, nq); p->scale *= 2.f; return ok; }
+  if (r == "mix.k") { const bool ok = seg(L.off_k, nq); p->scale *= 2.f; return ok; }
+  if (r == "mix.v") { const bool ok = seg(L.off_v, nv); p->scale *= 2.f; return ok; }
+  if (r == "mix.b") return seg(L.off_b, H);
+  if (r == "mix.a1") return seg(L.off_a1, s.rank_decay);
+  if (r == "mix.g1") return seg(L.off_g1, s.rank_gate);
+  if (r == "mix.a2") return mat(L.w_a2, (int64_t)H * DK, s.rank_decay);
+  if (r == "mix.g2") return mat(L.w_g2, nv, s.rank_gate);
+  if (r == "mix.norm") return vec(L.mix_norm, DV, 1.f, 0.1f);
+  if (r == "mix.A_log") return vec(L.A_log, H, 0.f, 0.5f);
+  if (r == "mix.dt_bias") return vec(L.dt_bias, (int64_t)H * DK, -1.f, 0.5f);
+  auto conv = [&](int ch0, int64_t rows) {
+    p->dst = L.conv_w + (size_t)ch0 * s.conv_taps; p->wt = false; p->rows = rows; p->cols = s.conv_taps; p->ld = s.conv_taps;
+    p->scale = 1.0f / sqrtf((float)s.conv_taps);
+    return true;
+  };
+  if (r == "mix.q.conv") return conv(0, nq);
+  if (r == "mix.k.conv") return conv(nq, nq);
+  if (r == "mix.v.conv") return conv(2 * nq, nv);
+  return false;
+}
+
+static std::vector<std::string> ll_expected(const L3Model* m) {
+  const LayerList* ll = m->ll;
+  std::vector<std::string> v = {"embed", "head", "final.norm"};
+  if (ll->cfg.side_dim) v.push_back("side.embed");
+  for (int i = 0; i < ll->cfg.n_layers; ++i) {
+    const L3LayerSpec& s = ll->layers[i].spec;
+    const std::string p = "l" + std::to_string(i) + ".";
+    std::vector<const char*> names = {"norm1", "mix.o"};
+    if (s.mixer == L3_MIX_SOFTMAX) names.insert(names.end(), {"mix.q", "mix.k", "mix.g", "mix.q.norm", "mix.k.norm"});
+    else if (s.mixer == L3_MIX_DECAY_LINEAR) names.insert(names.end(), {"mix.q", "mix.k", "mix.v", "mix.g", "mix.norm"});
+    else names.insert(names.end(), {"mix.q", "mix.k", "mix.v", "mix.b", "mix.a1", "mix.a2", "mix.g1", "mix.g2", "mix.norm",
+                                    "mix.A_log", "mix.dt_bias", "mix.q.conv", "mix.k.conv", "mix.v.conv"});
+    if (s.ff > 0) names.insert(names.end(), {"norm2", "mlp.gate", "mlp.up", "mlp.down"});
+    if (ll->cfg.side_dim) names.insert(names.end(), {"side.gate", "side.proj", "side.norm"});
+    for (auto nme : names) v.push_back(p + nme);
+  }
+  return v;
+}
+
+extern "C" int l3_load_tensor(L3Model* m, const char* name, const float* host, const int64_t* shape, int ndim) {
+  if (!m) return L3_EINVAL;
+  REQUIRE(m, m->ll != nullptr, "l3_load_tensor needs a handle made by l3_create_stack");
+  REQUIRE(m, !m->finalized, "l3_load_tensor after l3_finalize");
+  CK(m, cudaSetDevice(m->cfg.device));
+  LLPlace p;
+  REQUIRE(m, ll_place(m, name, &p), "tensor '%s' does not belong to this model", name);
+  REQUIRE(m, ndim == 1 || ndim == 2, "'%s': expected a vector or a matrix, got %d dimensions", name, ndim);
+  const int64_t rows = shape[0], cols = ndim > 1 ? shape[1] : 1;
+  REQUIRE(m, rows == p.rows && cols == p.cols, "shape mismatch for '%s': got [%lld, %lld], want [%lld, %lld]", name,
+          (long long)rows, (long long)cols, (long long)p.rows, (long long)p.cols);
+  const size_t STAGE = (size_t)256 << 20;
+  if (!m->stage) CK(m, cudaMalloc((void**)&m->stage, STAGE));
+  const int64_t rows_per = std::max<int64_t>(1, (int64_t)(STAGE / (cols * sizeof(float))));
+  for (int64_t r0 = 0; r0 < rows; r0 += rows_per) {
+    const int64_t nr = std::min(rows_per, rows - r0);
+    CK(m, cudaMemcpyAsync(m->stage, host + r0 * cols, (size_t)nr * cols * sizeof(float), cudaMemcpyHostToDevice, m->stream));
+    CK(m, launch_pack_rows(m->stage, (int)nr, (int)cols, p.dst, p.wt && m->bf16, p.row0 + (int)r0 * p.row_stride, p.row_stride,
+                           p.ld, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+  }
+  if (p.one_plus) {
+    CK(m, launch_add_one((float*)p.dst, (int)rows, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+  }
+  m->ll->loaded.insert(name);
+  return L3_OK;
+}
+
+// l3_fill_random for a layer-list handle: every expected tensor, deterministic in (seed, tensor index)
+int ll_fill_random(L3Model* m, uint64_t seed) {
+  uint32_t id = 1;
+  for (const auto& name : ll_expected(m)) {
+    LLPlace p;
+    if (!ll_place(m, name, &p)) { set_err(m, "no place for '%s'", name.c_str()); return L3_ESTATE; }
+    const float bias = p.one_plus ? p.bias + 1.0f : p.bias;
+    CK(m, launch_fill_random(p.dst, p.wt && m->bf16, p.rows, p.cols, p.cols, 0, 0, p.row0, p.row_stride, p.ld, seed, id++,
+                             p.scale, bias, m->stream));
+    m->ll->loaded.insert(name);
+  }
+  CK(m, cudaStreamSynchronize(m->stream));
+  return L3_OK;
+}
+
+// ------------------------------------------------------------------------------ finalize / destroy / state
+int ll_finalize(L3Model* m) {
+  LayerList* ll = m->ll;
+  for (const auto& name : ll_expected(m))
+    if (!ll->loaded.count(name)) { set_err(m, "tensor '%s' was never loaded", name.c_str()); return L3_ESTATE; }
+  if (m->stage) { cudaFree(m->stage); m->stage = nullptr; }
+  const size_t kvb = m->bf16 ? 2 : 4;
+  int max_rq = 1, max_rk = 1, max_rv = 1, max_rg = 1, max_h = 1, max_aux = 1;
+  for (auto& L : ll->layers) {
+    const L3LayerSpec& s = L.spec;
+    const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
+    if (s.mixer == L3_MIX_SOFTMAX) {
+      const size_t bytes = (size_t)m->maxB * G * m->M * DK * kvb;
+      CK(m, cudaMalloc(&L.ck, bytes));
+      CK(m, cudaMalloc(&L.cv, bytes));
+      max_rq = std::max(max_rq, H * DK);
+    } else {
+      CK(m, cudaMalloc((void**)&L.S, (size_t)m->maxB * H * DK * DV * 4));
+      if (s.mixer == L3_MIX_GATED_DELTA) {
+        const int C = 2 * G * DK + H * DV;
+        CK(m, cudaMalloc((void**)&L.conv_tail, std::max<size_t>(16, (size_t)m->maxB * C * (s.conv_taps - 1) * 4)));
+        max_rq = std::max(max_rq, G * DK); max_rk = std::max(max_rk, G * DK); max_rv = std::max(max_rv, H * DV);
+        max_rg = std::max(max_rg, H * DK); max_h = std::max(max_h, H); max_aux = std::max(max_aux, H * DK + H * DV);
+      }
+    }
+  }
+  const int W = m->D, sd = ll->cfg.side_dim;
+  const int64_t want = (int64_t)m->maxB * m->M;
+  m->cap_tok = (int)std::max<int64_t>(m->maxB, std::min<int64_t>(want, 8192));
+  const size_t ct = (size_t)m->cap_tok;
+  CK(m, cudaMalloc((void**)&m->x, ct * W * 4));
+  CK(m, cudaMalloc((void**)&m->xn, ct * W * 4));  // sublayer output before its norm
+  CK(m, cudaMalloc((void**)&m->q, ct * max_rq * 4));
+  CK(m, cudaMalloc((void**)&m->ctx, ct * ll->max_o * 4));
+  CK(m, cudaMalloc((void**)&m->h, ct * std::max(1, ll->max_ff) * 4));
+  CK(m, cudaMalloc((void**)&m->xlast, (size_t)m->maxB * W * 4));
+  CK(m, cudaMalloc((void**)&m->logits, (size_t)m->maxB * m->VS * 4));
+  CK(m, cudaMalloc((void**)&ll->pin, ct * ll->max_in * 4));
+  CK(m, cudaMalloc((void**)&ll->aux, ct * max_aux * 4));
+  CK(m, cudaMalloc((void**)&ll->rk, ct * max_rk * 4));
+  CK(m, cudaMalloc((void**)&ll->rv, ct * max_rv * 4));
+  CK(m, cudaMalloc((void**)&ll->rg, ct * max_rg * 4));
+  CK(m, cudaMalloc((void**)&ll->rbeta, ct * max_h * 4));
+  CK(m, cudaMalloc((void**)&ll->o, ct * ll->max_o * 4));
+  CK(m, cudaMalloc((void**)&ll->sg, ct * std::max(1, sd) * 4));
+  // tensor cores: bf16 mode only.  fp32 mode is the exact mode of this family: every product is an fp32 FFMA chain
+  // (the 3xTF32 scheme of the Llama path would need a (hi, lo) copy of the residual stream beside the stream itself).
+  m->tc_ok = m->bf16 && !(m->cfg.flags & L3_FLAG_NO_TENSORCORE) && tc_gemm_supported(W);
+  if (m->tc_ok) {
+    if (!(getenv("L3_GEMM_KSPLIT") && atoi(getenv("L3_GEMM_KSPLIT")) == 0)) {
+      CK(m, cudaMalloc((void**)&m->gemm_part, (size_t)32 << 20));
+      CK(m, cudaMalloc((void**)&m->gemm_cnt, 1024 * sizeof(int)));
+      CK(m, cudaMemsetAsync(m->gemm_cnt, 0, 1024 * sizeof(int), m->stream));
+    }
+    CK(m, cudaMalloc(&m->xn16, ct * W * 2));  // mirror of the residual stream
+    CK(m, cudaMalloc(&m->ctx16, ct * ll->max_o * 2));
+    CK(m, cudaMalloc(&m->h16, ct * std::max(1, ll->max_ff) * 2));
+    CK(m, cudaMalloc(&m->xlast16, (size_t)m->maxB * W * 2));
+    CK(m, cudaMalloc(&ll->sg16, ct * std::max(1, sd) * 2));
+  }
+  m->max_split = 32;
+  int max_hn = 1, max_hd = 1;
+  for (auto& L : ll->layers)
+    if (L.spec.mixer == L3_MIX_SOFTMAX) { max_hn = std::max(max_hn, L.spec.heads); max_hd = std::max(max_hd, L.spec.dim); }
+  CK(m, cudaMalloc((void**)&m->part_o, (size_t)m->maxB * max_hn * m->max_split * max_hd * 4));
+  CK(m, cudaMalloc((void**)&m->part_ml, (size_t)m->maxB * max_hn * m->max_split * 2 * 4));
+  CK(m, cudaMalloc((void**)&m->attn_cnt, (size_t)m->maxB * max_hn * 4));
+  CK(m, cudaMemsetAsync(m->attn_cnt, 0, (size_t)m->maxB * max_hn * 4, m->stream));
+  CK(m, cudaMalloc((void**)&m->d_ids, (size_t)m->maxB * m->M * 4));
+  CK(m, cudaMalloc((void**)&m->d_next, (size_t)m->maxB * 4));
+  CK(m, cudaMalloc((void**)&m->d_fwd_next, (size_t)m->maxB * 4));
+  CK(m, cudaMalloc((void**)&m->d_fwd_ids, (size_t)m->maxB * m->M * 4));
+  CK(m, cudaMalloc((void**)&m->d_scal, 16 * 4));
+  CK(m, cudaMemsetAsync(m->d_scal, 0, 16 * 4, m->stream));
+  CK(m, cudaMalloc((void**)&m->d_tokens, (size_t)m->maxB * m->M * 8));
+  CK(m, cudaMalloc((void**)&m->d_fwd_arg, (size_t)m->maxB * 8));
+  CK(m, cudaMalloc((void**)&m->d_best, (size_t)m->maxB * 8));
+  CK(m, cudaMemsetAsync(m->d_best, 0, (size_t)m->maxB * 8, m->stream));
+  CK(m, cudaMallocHost((void**)&m->h_next, (size_t)m->maxB * 4));
+  cudaDeviceProp prop;
+  CK(m, cudaGetDeviceProperties(&prop, m->cfg.device));
+  m->n_sm = prop.multiProcessorCount;
+  ll->head_rows = m->maxB;
+  m->finalized = true;
+  const int rc = ll_reset_slots(m, 0, m->maxB, true);
+  if (rc != L3_OK) { m->finalized = false; return rc; }
+  CK(m, cudaStreamSynchronize(m->stream));
+  return L3_OK;
+}
+
+void ll_destroy(L3Model* m) {
+  LayerList* ll = m->ll;
+  if (!ll) return;
+  auto fr = [](void* p) { if (p) cudaFree(p); };
+  fr(ll->side_embed);
+  for (auto& L : ll->layers) {
+    fr(L.w_in); fr(L.w_o); fr(L.w_a2); fr(L.w_g2); fr(L.w13); fr(L.w2); fr(L.side_gate); fr(L.side_proj);
+    fr(L.norm1); fr(L.norm2); fr(L.side_norm); fr(L.mix_norm); fr(L.q_norm); fr(L.k_norm); fr(L.conv_w);
+    fr(L.A_log); fr(L.dt_bias); fr(L.decay); fr(L.ck); fr(L.cv); fr(L.S); fr(L.conv_tail);
+  }
+  fr(ll->pin); fr(ll->aux); fr(ll->rk); fr(ll->rv); fr(ll->rg); fr(ll->rbeta); fr(ll->o); fr(ll->sg); fr(ll->sg16);
+  delete ll;
+  m->ll = nullptr;
+}
+
+int ll_reset_slots(L3Model* m, int slot0, int n, bool kv_too) {
+  LayerList* ll = m->ll;
+  const size_t kvb = m->bf16 ? 2 : 4;
+  for (auto& L : ll->layers) {
+    const L3LayerSpec& s = L.spec;
+    if (s.mixer == L3_MIX_SOFTMAX) {
+      if (!kv_too) continue;  // rows past a slot's position are never read: a new sequence overwrites them
+      const size_t per = (size_t)s.kv_heads * m->M * s.dim * kvb;
+      CK(m, cudaMemsetAsync((char*)L.ck + slot0 * per, 0, n * per, m->stream));
+      CK(m, cudaMemsetAsync((char*)L.cv + slot0 * per, 0, n * per, m->stream));
+    } else {
+      const size_t per = (size_t)s.heads * s.dim * s.vdim;
+      CK(m, cudaMemsetAsync(L.S + slot0 * per, 0, n * per * 4, m->stream));
+      if (s.mixer == L3_MIX_GATED_DELTA && s.conv_taps > 1) {
+        const size_t pc = (size_t)(2 * s.kv_heads * s.dim + s.heads * s.vdim) * (s.conv_taps - 1);
+        CK(m, cudaMemsetAsync(L.conv_tail + slot0 * pc, 0, n * pc * 4, m->stream));
+      }
+    }
+  }
+  for (int b = slot0; b < slot0 + n; ++b) ll->slot_pos[b] = 0;
+  return L3_OK;
+}
+
+int ll_begin_call(L3Model* m, int B, int L, int start_pos) {
+  LayerList* ll = m->ll;
+  if (start_pos == 0) {
+    const int rc = ll_reset_slots(m, 0, B, false);
+    if (rc != L3_OK) return rc;
+  } else {
+    for (int b = 0; b < B; ++b)
+      if (ll->slot_pos[b] != start_pos) {
+        set_err(m, "slot %d is at position %d, the call starts at %d: a recurrent state cannot be moved", b, ll->slot_pos[b], start_pos);
+        return L3_ESTATE;
+      }
+  }
+  for (int b = 0; b < B; ++b) ll->slot_pos[b] = start_pos + L;
+  return L3_OK;
+}
+
+extern "C" int l3_read_state(L3Model* m, int layer, int slot, float* S_out, float* conv_out) {
+  if (!m || !m->finalized) return L3_ESTATE;
+  REQUIRE(m, m->ll != nullptr, "l3_read_state needs a handle made by l3_create_stack");
+  REQUIRE(m, layer >= 0 && layer < m->cfg.n_layers && slot >= 0 && slot < m->maxB, "layer / slot out of range");
+  const LLLayer& L = m->ll->layers[layer];
+  const L3LayerSpec& s = L.spec;
+  REQUIRE(m, s.mixer != L3_MIX_SOFTMAX, "layer %d keeps a KV cache, not a recurrent state (l3_read_cache)", layer);
+  CK(m, cudaSetDevice(m->cfg.device));
+  CK(m, cudaStreamSynchronize(m->stream));
+  const size_t per = (size_t)s.heads * s.dim * s.vdim;
+  if (S_out) CK(m, cudaMemcpy(S_out, L.S + slot * per, per * 4, cudaMemcpyDeviceToHost));
+  if (conv_out) {
+    REQUIRE(m, s.mixer == L3_MIX_GATED_DELTA, "layer %d has no convolution", layer);
+    const size_t pc = (size_t)(2 * s.kv_heads * s.dim + s.heads * s.vdim) * (s.conv_taps - 1);
+    if (pc) CK(m, cudaMemcpy(conv_out, L.conv_tail + slot * pc, pc * 4, cudaMemcpyDeviceToHost));
+  }
+  return L3_OK;
+}
+
+// ------------------------------------------------------------------------------ projections
+// y = x W^T (+ epilogue).  x32: fp32 rows with stride lda (0 = K); x16: bf16 mirror with stride K, or null.
+static int ll_linear(L3Model* m, const void* W, const float* x32, const void* x16, int lda, int rows, int N, int K, int epi,
+                     const EpiArgs& e) {
+  LinearArgs a{};
+  a.W = W; a.x = x32; a.lda = lda; a.rows = rows; a.N = N; a.K = K; a.src_mul = 1; a.src_add = 0; a.epi = epi; a.e = e;
+  const int ld = lda ? lda : K;
+  if (linear_rows_supported(rows, K) && ld % 4 == 0) {
+    LAUNCH(m, launch_linear_rows(a, m->bf16, m->bf16, m->stream));
+    return L3_OK;
+  }
+  if (m->tc_ok && x16 && ld == K && K % 8 == 0 && K >= 64 && N >= 64) {
+    TcGemmArgs t{};
+    t.kind = TC_BF16; t.A[0] = x16; t.W[0] = W;
+    t.rows = rows; t.N = N; t.K = K; t.epi = epi; t.e = e; t.bn = 0;
+    t.part = m->gemm_part; t.part_bytes = (size_t)32 << 20; t.tile_cnt = m->gemm_cnt; t.tile_cnt_len = 1024;
+    static const bool swap_on = !(getenv("L3_GEMM_SWAP") && atoi(getenv("L3_GEMM_SWAP")) == 0);
+    if (swap_on && gemm_swap_supported(rows, N)) LAUNCH(m, launch_gemm_swap(t, m->stream));
+    else LAUNCH(m, launch_gemm_tc(t, m->stream));
+    return L3_OK;
+  }
+  if (K % 4 == 0 && ld % 4 == 0) LAUNCH(m, launch_linear_simt(a, m->bf16, m->bf16, m->stream));
+  else LAUNCH(m, launch_linear_any(a, m->bf16, m->stream));
+  return L3_OK;
+}
+
+static EpiArgs store_to(float* out, void* out16, int ld) {
+  EpiArgs e{};
+  e.out = out; e.out_bf16 = (bf16*)out16; e.ld_out = ld;
+  return e;
+}
+
+// ------------------------------------------------------------------------------ the layers of one chunk
+int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off, int B, int L, float* d_resid) {
+  LayerList* ll = m->ll;
+  const int ntok = B * L, W = m->D, sd = ll->cfg.side_dim;
+  const float eps = ll->cfg.norm_eps, mult = ll->cfg.residual_mult;
+  int* d_pos = m->d_scal + 0;
+  bf16* x16 = (bf16*)m->xn16;  // null in fp32 mode
+  float* y = m->xn;
+  int rc;
+  if (x16) LAUNCH(m, launch_to_bf16(m->x, (int64_t)ntok * W, x16, m->stream));
+  for (int li = 0; li < (int)ll->layers.size(); ++li) {
+    LLLayer& Ly = ll->layers[li];
+    const L3LayerSpec& s = Ly.spec;
+    const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim, O = H * DV;
+    // every projection of the mixer's input in one GEMM
+    if ((rc = ll_linear(m, Ly.w_in, m->x, x16, 0, ntok, Ly.n_in, W, EPI_STORE, store_to(ll->pin, nullptr, Ly.n_in))) != L3_OK) return rc;
+    if (s.mixer == L3_MIX_SOFTMAX) {
+      QkNormArgs qa{};
+      qa.proj = ll->pin; qa.ld = Ly.n_in; qa.k_off = Ly.off_k; qa.wq = Ly.q_norm; qa.wk = Ly.k_norm; qa.eps = eps;
+      qa.q_out = m->q; qa.cache_k = Ly.ck; qa.cache_v = Ly.cv; qa.pos_ptr = d_pos;
+      qa.L = L; qa.HN = H; qa.KVHN = G; qa.HD = DK; qa.M = m->M;
+      LAUNCH(m, launch_qk_norm_cache(qa, ntok, m->bf16, m->stream));
+      AttnArgs at{};
+      at.q = m->q; at.cache_k = Ly.ck; at.cache_v = Ly.cv; at.pos_ptr = d_pos;
+      at.B = B; at.L = L; at.HN = H; at.KVHN = G; at.HD = DK; at.M = m->M;
+      at.part_o = m->part_o; at.part_ml = m->part_ml; at.counters = m->attn_cnt;
+      at.out = m->ctx; at.out_bf16 = (bf16*)m->ctx16;
+      at.scale = s.scale; at.head_gate = ll->pin + Ly.off_g; at.ld_gate = Ly.n_in;
+      at.force_exact = 1;  // scores and softmax weights stay fp32
+      at.nsplit = 1;
+      if (!attn_head_dim_supported(DK)) LAUNCH(m, launch_attn_any(at, m->bf16, m->stream));
+      else if (L == 1) {
+        at.nsplit = std::max(1, std::min(std::min(m->max_split, m->M / 16), (4 * 148) / std::max(1, B * G)));
+        LAUNCH(m, launch_attn_decode(at, m->bf16, m->stream));
+      } else LAUNCH(m, launch_attn_prefill(at, m->bf16, m->stream));
+    } else if (s.mixer == L3_MIX_DECAY_LINEAR) {
+      RecurArgs ra{};
+      ra.mode = 0; ra.q = ll->pin + Ly.off_q; ra.k = ll->pin + Ly.off_k; ra.v = ll->pin + Ly.off_v;
+      ra.ld_q = ra.ld_k = ra.ld_v = Ly.n_in; ra.act_in = 1; ra.head_decay = Ly.decay;
+      ra.state = Ly.S; ra.out = ll->o; ra.B = B; ra.L = L; ra.H = H; ra.rep = 1; ra.DK = DK; ra.DV = DV;
+      LAUNCH(m, launch_recur(ra, m->stream));
+      LAUNCH(m, launch_gated_rmsnorm(ll->o, ll->pin + Ly.off_g, Ly.n_in, Ly.mix_norm, O, O, eps, ntok, O, m->ctx, (bf16*)m->ctx16, m->stream));
+    } else {
+      const int nq = G * DK, nd = H * DK;
+      float* dt = ll->aux;                          // [ntok, H * DK] decay logits
+      float* og = ll->aux + (size_t)ntok * nd;      // [ntok, H * DV] output-gate logits
+      if ((rc = ll_linear(m, Ly.w_a2, ll->pin + Ly.off_a1, nullptr, Ly.n_in, ntok, nd, s.rank_decay, EPI_STORE, store_to(dt, nullptr, nd))) != L3_OK) return rc;
+      if ((rc = ll_linear(m, Ly.w_g2, ll->pin + Ly.off_g1, nullptr, Ly.n_in, ntok, O, s.rank_gate, EPI_STORE, store_to(og, nullptr, O))) != L3_OK) return rc;
+      DeltaPrepArgs pa{};
+      pa.proj = ll->pin; pa.ld = Ly.n_in; pa.beta_off = Ly.off_b; pa.dt_in = dt; pa.ld_dt = nd;
+      pa.conv_w = Ly.conv_w; pa.conv_tail = Ly.conv_tail; pa.A_log = Ly.A_log; pa.dt_bias = Ly.dt_bias;
+      pa.q_out = m->q; pa.k_out = ll->rk; pa.v_out = ll->rv; pa.decay_out = ll->rg; pa.beta_out = ll->rbeta;
+      pa.L = L; pa.H = H; pa.G = G; pa.DK = DK; pa.DV = DV; pa.taps = s.conv_taps;
+      LAUNCH(m, launch_delta_prep(pa, ntok, m->stream));
+      if (s.conv_taps > 1) LAUNCH(m, launch_conv_tail(Ly.conv_tail, ll->pin, Ly.n_in, B, L, 2 * nq + O, s.conv_taps - 1, m->stream));
+      RecurArgs ra{};
+      ra.mode = 1; ra.q = m->q; ra.k = ll->rk; ra.v = ll->rv; ra.ld_q = ra.ld_k = nq; ra.ld_v = O;
+      ra.g = ll->rg; ra.beta = ll->rbeta; ra.state = Ly.S; ra.out = ll->o;
+      ra.B = B; ra.L = L; ra.H = H; ra.rep = H / G; ra.DK = DK; ra.DV = DV;
+      LAUNCH(m, launch_recur(ra, m->stream));
+      LAUNCH(m, launch_gated_rmsnorm(ll->o, og, O, Ly.mix_norm, DV, DV, eps, ntok, O, m->ctx, (bf16*)m->ctx16, m->stream));
+    }
+    if ((rc = ll_linear(m, Ly.w_o, m->ctx, m->ctx16, 0, ntok, W, O, EPI_STORE, store_to(y, nullptr, W))) != L3_OK) return rc;
+    LAUNCH(m, launch_resid_postnorm(m->x, y, Ly.norm1, mult, eps, ntok, W, x16, m->stream));
+    if (s.ff > 0) {
+      EpiArgs e = store_to(m->h, m->h16, s.ff);
+      e.act = ll->cfg.glu_act;
+      if ((rc = ll_linear(m, Ly.w13, m->x, x16, 0, ntok, 2 * s.ff, W, EPI_SWIGLU, e)) != L3_OK) return rc;
+      if ((rc = ll_linear(m, Ly.w2, m->h, m->h16, 0, ntok, W, s.ff, EPI_STORE, store_to(y, nullptr, W))) != L3_OK) return rc;
+      LAUNCH(m, launch_resid_postnorm(m->x, y, Ly.norm2, mult, eps, ntok, W, x16, m->stream));
+    }
+    if (sd) {
+      if ((rc = ll_linear(m, Ly.side_gate, m->x, x16, 0, ntok, sd, W, EPI_STORE, store_to(ll->sg, nullptr, sd))) != L3_OK) return rc;
+      LAUNCH(m, launch_side_mul(ll->sg, sd, ntok, ll->side_embed, m->bf16, (int)ll->layers.size() * sd, li * sd, d_ids, ids_ld, ids_off, L,
+                                m->cfg.vocab_size, ll->cfg.glu_act, (bf16*)ll->sg16, m->stream));
+      if ((rc = ll_linear(m, Ly.side_proj, ll->sg, ll->sg16, 0, ntok, W, sd, EPI_STORE, store_to(y, nullptr, W))) != L3_OK) return rc;
+      LAUNCH(m, launch_resid_postnorm(m->x, y, Ly.side_norm, mult, eps, ntok, W, x16, m->stream));
+    }
+    if (d_resid)
+      CK(m, cudaMemcpyAsync(d_resid + (size_t)li * ntok * W, m->x, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));
+  }
+  return L3_OK;
+}
+
+int ll_ensure_head_rows(L3Model* m, int n) {
+  LayerList* ll = m->ll;
+  if (n <= ll->head_rows) return L3_OK;
+  CK(m, cudaStreamSynchronize(m->stream));
+  cudaFree(m->xlast); cudaFree(m->logits);
+  m->xlast = m->logits = nullptr;
+  CK(m, cudaMalloc((void**)&m->xlast, (size_t)n * m->D * 4));
+  CK(m, cudaMalloc((void**)&m->logits, (size_t)n * m->VS * 4));
+  if (m->xlast16) {
+    cudaFree(m->xlast16);
+    m->xlast16 = nullptr;
+    CK(m, cudaMalloc(&m->xlast16, (size_t)n * m->D * 2));
+  }
+  ll->head_rows = n;
+  return L3_OK;
+}
+
+int ll_enqueue_head(L3Model* m, int B, int L, const int32_t* d_rows, int n_rows) {
+  const int rows = d_rows ? n_rows : B;
+  LAUNCH(m, launch_rmsnorm_rows(m->x, m->norm_final, m->ll->cfg.norm_eps, rows, m->D, L, L - 1, d_rows, m->xlast, (bf16*)m->xlast16, m->stream));
+  return ll_linear(m, m->lm_head, m->xlast, m->xlast16, 0, rows, m->VS, m->D, EPI_STORE, store_to(m->logits, nullptr, m->VS));
+}

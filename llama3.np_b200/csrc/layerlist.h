@@ -1,0 +1,65 @@
+// Layer-list decoders (l3_create_stack, include/llama3_b200.h): a decoder described as a list of layers, each
+// with its own token mixer, an optional gated feed-forward and an optional per-layer token input, sharing the
+// handle, the entry points, the generate loop, the graphs and the projection kernels of the Llama path.
+#pragma once
+#include <set>
+#include <string>
+#include <vector>
+
+#include "model.h"
+
+struct LLLayer {
+  L3LayerSpec spec{};
+  // ---- weights (WT = model dtype unless noted)
+  void* w_in = nullptr;    // [n_in, width]: every projection that reads the mixer's input, fused row-wise
+  int n_in = 0;
+  // row / column offsets of the segments inside w_in / its output
+  int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_b = 0, off_a1 = 0, off_g1 = 0;
+  void* w_o = nullptr;     // [width, heads * vdim]
+  void* w_a2 = nullptr;    // gated delta: [heads * dim, rank_decay]
+  void* w_g2 = nullptr;    // gated delta: [heads * vdim, rank_gate]
+  void* w13 = nullptr;     // [2 ff, width] rows interleaved gate_j, up_j
+  void* w2 = nullptr;      // [width, ff]
+  void* side_gate = nullptr;  // [side_dim, width]
+  void* side_proj = nullptr;  // [width, side_dim]
+  // fp32 vectors
+  float *norm1 = nullptr, *norm2 = nullptr, *side_norm = nullptr;  // norm1 / norm2 hold 1 + w when norm_one_plus
+  float* mix_norm = nullptr;  // decay-linear: [heads * vdim]; gated delta: [vdim]
+  float *q_norm = nullptr, *k_norm = nullptr;  // softmax: over the whole projection
+  float* conv_w = nullptr;    // gated delta: [2 kv_heads dim + heads vdim, taps]
+  float *A_log = nullptr, *dt_bias = nullptr;
+  float* decay = nullptr;     // decay-linear: [heads]
+  // ---- state per sequence slot
+  void *ck = nullptr, *cv = nullptr;  // softmax: [maxB, kv_heads, M, dim] of KVT (cv = keys as projected)
+  float* S = nullptr;                 // recurrent: [maxB, heads, dim, vdim]
+  float* conv_tail = nullptr;         // gated delta: [maxB, channels, taps - 1]
+};
+
+struct LayerList {
+  L3StackConfig cfg{};
+  std::vector<LLLayer> layers;
+  void* side_embed = nullptr;  // [vocab, n_layers * side_dim] of WT
+  std::set<std::string> loaded;
+  std::vector<int> slot_pos;   // next position of every sequence slot (host copy)
+  // workspace beyond the shared buffers of L3Model (x, xn = sublayer output, q, ctx, h + bf16 mirrors)
+  float *pin = nullptr, *aux = nullptr, *rk = nullptr, *rv = nullptr, *rg = nullptr, *rbeta = nullptr, *o = nullptr;
+  float* sg = nullptr;
+  void* sg16 = nullptr;
+  int max_in = 0, max_o = 0, max_ff = 0;
+  int head_rows = 0;  // rows the LM head's buffers hold
+};
+
+int ll_fill_random(L3Model* m, uint64_t seed);
+// final norm + LM head over `rows` source rows of m->x (d_rows, or row b * L + L - 1 of every sequence) -> m->logits
+int ll_enqueue_head(L3Model* m, int B, int L, const int32_t* d_rows, int n_rows);
+// room for n rows in the LM head's buffers (xlast, its mirror, logits)
+int ll_ensure_head_rows(L3Model* m, int n);
+int ll_finalize(L3Model* m);
+void ll_destroy(L3Model* m);
+// zero the KV caches and recurrent state of slots [slot0, slot0 + n) (all layers)
+int ll_reset_slots(L3Model* m, int slot0, int n, bool kv_too);
+// position bookkeeping of a call that feeds L tokens to slots [0, B) at start_pos; start_pos 0 zeroes their state
+int ll_begin_call(L3Model* m, int B, int L, int start_pos);
+// all layers of one chunk; x in m->x (and its bf16 mirror) on entry and exit.  d_resid: null, or
+// [n_layers, B * L, width] receiving the residual stream after every layer
+int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off, int B, int L, float* d_resid);

@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(512) linear_rows_kernel(LinearArgs a) {
   for (int m = 0; m < MB; ++m) {
     float* dst = xs + (size_t)m * K;
     if (m < a.rows) {
-      const float* src = a.x + (a.src_rows ? (size_t)a.src_rows[m] : (size_t)m * a.src_mul + a.src_add) * K;
+      const float* src = a.x + (a.src_rows ? (size_t)a.src_rows[m] : (size_t)m * a.src_mul + a.src_add) * (a.lda ? a.lda : K);
       float ss = 0.f;
       for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {
         float4 v = *reinterpret_cast<const float4*>(src + k);
@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(256) linear_simt_kernel(LinearArgs a) {
   const int lrow = tid >> 2, lk = (tid & 3) * 4;
   const int arow = m0 + lrow, brow = n0 + lrow;
   const int arow_c = arow < M ? arow : 0;
-  const float* aptr = a.x + (a.src_rows ? (size_t)a.src_rows[arow_c] : (size_t)arow_c * a.src_mul + a.src_add) * K;
+  const float* aptr = a.x + (a.src_rows ? (size_t)a.src_rows[arow_c] : (size_t)arow_c * a.src_mul + a.src_add) * (a.lda ? a.lda : K);
   const WT* bptr = W + (size_t)(brow < N ? brow : 0) * K;
   float ra[4], rb[4];
   auto fetch = [&](int k0) {
@@ -327,4 +327,72 @@ static cudaError_t launch_simt_e(const LinearArgs& a, cudaStream_t s) {
 cudaError_t launch_linear_simt(const LinearArgs& a, bool w_bf16, bool kv_bf16, cudaStream_t s) {
   if (w_bf16) return kv_bf16 ? launch_simt_e<bf16, bf16>(a, s) : launch_simt_e<bf16, float>(a, s);
   return kv_bf16 ? launch_simt_e<float, bf16>(a, s) : launch_simt_e<float, float>(a, s);
+}
+
+// ============================================================================ any-shape GEMM
+// The same product for shapes the vector kernels above cannot take (K or the row stride of x not a
+// multiple of 4): 32 x 64 tile, BK = 32, scalar guarded loads, fp32 FFMA, the same epilogues.
+#define GA_BM 32
+#define GA_BN 64
+#define GA_BK 32
+template <typename WT, int EPI, typename KVT>
+__global__ void __launch_bounds__(256) linear_any_kernel(LinearArgs a) {
+  __shared__ float As[GA_BK][GA_BM + 1];
+  __shared__ float Bs[GA_BK][GA_BN + 1];
+  pdl_launch();
+  pdl_wait();
+  const int tid = threadIdx.x, ty = tid >> 5, tx = tid & 31;
+  const int m0 = blockIdx.y * GA_BM, n0 = blockIdx.x * GA_BN;
+  const int M = a.rows, N = a.N, K = a.K, lda = a.lda ? a.lda : a.K;
+  const WT* W = reinterpret_cast<const WT*>(a.W);
+  float acc[4][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+  for (int k0 = 0; k0 < K; k0 += GA_BK) {
+    for (int i = tid; i < GA_BM * GA_BK; i += 256) {
+      const int r = i / GA_BK, k = i % GA_BK, m = m0 + r;
+      float v = 0.f;
+      if (m < M && k0 + k < K) {
+        const size_t srow = a.src_rows ? (size_t)a.src_rows[m] : (size_t)m * a.src_mul + a.src_add;
+        v = a.x[srow * lda + k0 + k];
+      }
+      As[k][r] = v;
+    }
+    for (int i = tid; i < GA_BN * GA_BK; i += 256) {
+      const int r = i / GA_BK, k = i % GA_BK, n = n0 + r;
+      Bs[k][r] = (n < N && k0 + k < K) ? to_f32(W[(size_t)n * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < GA_BK; ++k) {
+      const float b0 = Bs[k][tx * 2], b1 = Bs[k][tx * 2 + 1];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float av = As[k][ty * 4 + i];
+        acc[i][0] = fmaf(av, b0, acc[i][0]);
+        acc[i][1] = fmaf(av, b1, acc[i][1]);
+      }
+    }
+    __syncthreads();
+  }
+  const int col = n0 + tx * 2;
+  if (col >= N) return;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m < M) epilogue_pair<KVT>(EPI, a.e, m, col, acc[i][0], acc[i][1], col + 1 < N);
+  }
+}
+
+template <typename WT>
+static cudaError_t launch_any_e(const LinearArgs& a, cudaStream_t s) {
+  dim3 grid((a.N + GA_BN - 1) / GA_BN, (a.rows + GA_BM - 1) / GA_BM);
+  switch (a.epi) {
+    case EPI_STORE: return launch_k(linear_any_kernel<WT, EPI_STORE, float>, grid, dim3(256), 0, s, a);
+    case EPI_RESID: return launch_k(linear_any_kernel<WT, EPI_RESID, float>, grid, dim3(256), 0, s, a);
+    case EPI_SWIGLU: return launch_k(linear_any_kernel<WT, EPI_SWIGLU, float>, grid, dim3(256), 0, s, a);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t launch_linear_any(const LinearArgs& a, bool w_bf16, cudaStream_t s) {
+  return w_bf16 ? launch_any_e<bf16>(a, s) : launch_any_e<float>(a, s);
 }

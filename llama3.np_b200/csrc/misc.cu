@@ -20,6 +20,10 @@ __global__ void embed_kernel(const WT* __restrict__ table, const int32_t* __rest
   const int id = min(max(ids[(size_t)b * ids_ld + ids_off + t], 0), vocab - 1);
   const WT* src = table + (size_t)id * D;
   float* dst = x + (size_t)r * D;
+  if (D & 3) {  // widths that are no multiple of 4: element by element
+    for (int k = threadIdx.x; k < D; k += blockDim.x) dst[k] = to_f32(src[k]);
+    return;
+  }
   for (int k = threadIdx.x * 4; k < D; k += blockDim.x * 4) {
     float4 o;
     o.x = to_f32(src[k]); o.y = to_f32(src[k + 1]); o.z = to_f32(src[k + 2]); o.w = to_f32(src[k + 3]);

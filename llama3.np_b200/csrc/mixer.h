@@ -1,0 +1,73 @@
+// Kernel-launch interface of the token mixers of layer-list decoders (mixer_ops.cu, recurrent.cu, attn_any.cu).
+#pragma once
+#include "common.cuh"
+
+// ---- row kernels (mixer_ops.cu)
+// x[r] += mult * y[r] / sqrt(mean(y[r]^2) + eps) * w; x16 (may be null) receives the bf16 mirror of the new x
+cudaError_t launch_resid_postnorm(float* x, const float* y, const float* w, float mult, float eps, int rows, int D,
+                                  bf16* x16, cudaStream_t s);
+// out[r, i] = o[r, i] / rms(group of i) * w[i % wlen] * sigmoid(gate[r * ld_gate + i]); group = O: one norm per row
+cudaError_t launch_gated_rmsnorm(const float* o, const float* gate, int ld_gate, const float* w, int wlen, int group,
+                                 float eps, int rows, int O, float* out, bf16* out16, cudaStream_t s);
+
+struct QkNormArgs {
+  const float* proj;   // [rows, ld]: q at column 0 (HN * HD), k at column k_off (KVHN * HD)
+  int ld, k_off;
+  const float* wq;     // [HN * HD], [KVHN * HD] plain norm weights over the whole projection
+  const float* wk;
+  float eps;
+  float* q_out;        // [rows, HN * HD] normalised q
+  void* cache_k;       // [maxB, KVHN, M, HD]: normalised k
+  void* cache_v;       // same shape: k as projected
+  const int* pos_ptr;  // device scalar: position of token 0 of every sequence in this call
+  int L, HN, KVHN, HD, M;
+};
+cudaError_t launch_qk_norm_cache(const QkNormArgs& a, int rows, bool kv_bf16, cudaStream_t s);
+
+// g[r, j] = act(g[r, j]) * table[token(r), col0 + j], in place (+ bf16 mirror)
+cudaError_t launch_side_mul(float* g, int n, int rows, const void* table, bool table_bf16, int table_ld, int col0,
+                            const int32_t* ids, int ids_ld, int ids_off, int L, int vocab, int act, bf16* out16,
+                            cudaStream_t s);
+
+struct DeltaPrepArgs {
+  const float* proj;      // [rows, ld]: q | k | v channels at columns [0, C), write-strength logits at beta_off
+  int ld, beta_off;
+  const float* dt_in;     // [rows, ld_dt]: decay logits per (head, key channel) before the bias
+  int ld_dt;
+  const float* conv_w;    // [C, taps], last tap = current token
+  const float* conv_tail; // [maxB, C, taps - 1]
+  const float* A_log;     // [H]
+  const float* dt_bias;   // [H * DK]
+  float *q_out, *k_out;   // [rows, G * DK]
+  float* v_out;           // [rows, H * DV]
+  float* decay_out;       // [rows, H * DK]
+  float* beta_out;        // [rows, H]
+  int L, H, G, DK, DV, taps;
+};
+cudaError_t launch_delta_prep(const DeltaPrepArgs& a, int rows, cudaStream_t s);
+cudaError_t launch_conv_tail(float* tail, const float* proj, int ld, int B, int L, int C, int T1, cudaStream_t s);
+// out[r] = x[src_rows ? src_rows[r] : r * src_mul + src_add] / rms * w  (+ bf16 mirror); any D
+cudaError_t launch_rmsnorm_rows(const float* x, const float* w, float eps, int rows, int D, int src_mul, int src_add,
+                                const int32_t* src_rows, float* out, bf16* out16, cudaStream_t s);
+cudaError_t launch_to_bf16(const float* in, int64_t n, bf16* out, cudaStream_t s);
+cudaError_t launch_add_one(float* p, int n, cudaStream_t s);
+
+// ---- recurrences over time (recurrent.cu): one fp32 state matrix [DK, DV] per (sequence slot, head)
+struct RecurArgs {
+  int mode;               // 0: S <- decay_h S + k v^T, o = S^T q  (q, k, v read through silu when act_in)
+                          // 1: S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q
+  const float *q, *k, *v; // rows [B * L, ld_*]; head h of q / k at column (h / rep) * DK, of v at column h * DV
+  int ld_q, ld_k, ld_v;
+  int act_in;             // 1: silu on q, k, v as they are read
+  const float* head_decay;  // mode 0: [H]
+  const float* g;         // mode 1: [B * L, H * DK]
+  const float* beta;      // mode 1: [B * L, H]
+  float* state;           // [maxB, H, DK, DV]
+  float* out;             // [B * L, H * DV]
+  int B, L, H, rep, DK, DV;
+};
+bool recur_supported(int DK, int DV);
+cudaError_t launch_recur(const RecurArgs& a, cudaStream_t s);
+
+// ---- attention for head sizes the tiled kernels do not take (attn_any.cu): same arguments, any HD
+cudaError_t launch_attn_any(const AttnArgs& a, bool kv_bf16, cudaStream_t s);

@@ -32,8 +32,11 @@ struct L3Graph {
   int64_t nodes = 0;
 };
 
+struct LayerList;  // layerlist.h: the layers, state and workspace of a layer-list decoder
+
 struct L3Model {
   L3Config cfg{};
+  LayerList* ll = nullptr;  // non-null: made by l3_create_stack; cfg holds the shared fields (dim = width, ...)
   bool bf16 = false;
   // local (per tensor-parallel rank) dimensions
   int D = 0, HD = 0, G = 1, HN = 0, KVHN = 0, FD = 0, VS = 0, M = 0, maxB = 0, qkv_rows = 0;

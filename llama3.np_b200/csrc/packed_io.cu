@@ -96,6 +96,7 @@ struct Pinned {
 
 extern "C" int l3_save_packed(L3Model* m, const char* path, const char* source_digest) {
   if (!m || !path) return L3_EINVAL;
+  if (m->ll) PK_FAIL(m, L3_EINVAL, "the packed weight cache holds Llama handles only");
   for (size_t i = 0; i < m->loaded.size(); ++i)
     if (!m->loaded[i]) PK_FAIL(m, L3_ESTATE, "l3_save_packed: weight slot %zu was never loaded", i);
   PK_CUDA(m, cudaSetDevice(m->cfg.device));
@@ -177,6 +178,7 @@ extern "C" int l3_packed_info(const char* path, L3Config* cfg_out, char* digest_
 
 extern "C" int l3_load_packed(L3Model* m, const char* path, const char* source_digest) {
   if (!m || !path) return L3_EINVAL;
+  if (m->ll) PK_FAIL(m, L3_EINVAL, "the packed weight cache holds Llama handles only");
   if (m->finalized) PK_FAIL(m, L3_ESTATE, "l3_load_packed after l3_finalize");
   PK_CUDA(m, cudaSetDevice(m->cfg.device));
   File f;

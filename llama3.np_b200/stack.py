@@ -1,0 +1,241 @@
+"""Layer-list decoders on the C-ABI's stack handles (`l3_create_stack`, include/llama3_b200.h).
+
+`StackDecoder` is the host side every such model shares: the handle's lifetime, tensors by checkpoint
+name, the forward call (logits of the last token, or of chosen rows), the greedy generate loop of the
+library (CUDA-graph replays, next ids on the device) and the per-slot state rules - a call at
+`start_pos` 0 starts its sequence slots afresh, any other call continues them.  A model family (e.g.
+`risalix.Risalix`) only turns its configuration into a `StackConfig` and a list of `LayerSpec`s.
+The reference has one fixed block (llama3.py:238-262) and no counterpart of this.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Mapping, Optional, Sequence
+
+import numpy as np
+
+from . import _cabi
+
+SOFTMAX, DECAY_LINEAR, GATED_DELTA = _cabi.MIX_SOFTMAX, _cabi.MIX_DECAY_LINEAR, _cabi.MIX_GATED_DELTA
+_DTYPES = {"float32": _cabi.DTYPE_F32, "fp32": _cabi.DTYPE_F32, "bfloat16": _cabi.DTYPE_BF16, "bf16": _cabi.DTYPE_BF16}
+
+
+@dataclass
+class LayerSpec:
+    mixer: int                    # SOFTMAX | DECAY_LINEAR | GATED_DELTA
+    heads: int
+    dim: int
+    vdim: int
+    kv_heads: int = 0             # 0: = heads
+    conv_taps: int = 0            # GATED_DELTA
+    rank_decay: int = 0           # GATED_DELTA: inner width of the decay projection pair
+    rank_gate: int = 0            # GATED_DELTA: inner width of the output-gate projection pair
+    ff: int = 0                   # 0: no feed-forward in this layer
+    scale: float = 0.0            # SOFTMAX: multiplier of q . k
+    decay: Sequence[float] = ()   # DECAY_LINEAR: one per head
+
+
+@dataclass
+class StackConfig:
+    width: int
+    vocab: int
+    layers: List[LayerSpec] = field(default_factory=list)
+    norm_eps: float = 1e-5
+    residual_mult: float = 1.0
+    norm_one_plus: bool = True
+    glu_act: str = "gelu_tanh"    # "silu" | "gelu_tanh"
+    side_dim: int = 0
+    max_seq_len: int = 256
+    max_batch_size: int = 1
+    dtype: str = "float32"
+
+
+class StackDecoder:
+    def __init__(self, cfg: StackConfig, *, device: int = 0, flags: int = 0):
+        if cfg.dtype not in _DTYPES:
+            raise ValueError(f"unsupported dtype {cfg.dtype!r}; use 'float32' or 'bfloat16'")
+        if cfg.glu_act not in ("silu", "gelu_tanh"):
+            raise ValueError(f"unsupported activation {cfg.glu_act!r}")
+        self.cfg = cfg
+        self._lib = _cabi.lib()
+        self._h = C.c_void_p()
+        self._finalized = False
+        specs = (_cabi.L3LayerSpec * len(cfg.layers))()
+        keep = []
+        for i, l in enumerate(cfg.layers):
+            dec = (C.c_float * max(1, len(l.decay)))(*[float(x) for x in l.decay])
+            keep.append(dec)
+            if l.mixer == DECAY_LINEAR and len(l.decay) != l.heads:
+                raise ValueError(f"layer {i}: {len(l.decay)} decays for {l.heads} heads")
+            specs[i] = _cabi.L3LayerSpec(mixer=l.mixer, heads=l.heads, kv_heads=l.kv_heads or l.heads, dim=l.dim, vdim=l.vdim,
+                                         conv_taps=l.conv_taps, rank_decay=l.rank_decay, rank_gate=l.rank_gate, ff=l.ff,
+                                         scale=l.scale, decay=C.cast(dec, C.POINTER(C.c_float)) if len(l.decay) else None)
+        c = _cabi.L3StackConfig(width=cfg.width, vocab=cfg.vocab, n_layers=len(cfg.layers), max_seq_len=cfg.max_seq_len,
+                                max_batch_size=cfg.max_batch_size, dtype=_DTYPES[cfg.dtype], device=device, flags=flags,
+                                norm_eps=cfg.norm_eps, residual_mult=cfg.residual_mult, norm_one_plus=int(cfg.norm_one_plus),
+                                glu_act=_cabi.GLU_GELU_TANH if cfg.glu_act == "gelu_tanh" else _cabi.GLU_SILU,
+                                side_dim=cfg.side_dim)
+        _cabi.check(self._lib.l3_create_stack(C.byref(c), specs, C.byref(self._h)))
+
+    # ---------------------------------------------------------------- lifetime / weights
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self._lib.l3_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def load_tensors(self, tensors: Mapping[str, np.ndarray]) -> None:
+        """Upload every tensor of the mapping (checkpoint names) and finish the model.  Integer tables and other
+        names the model does not know are an error, as is a missing tensor."""
+        try:
+            for name in tensors.keys():
+                w = np.ascontiguousarray(tensors[name], dtype=np.float32)
+                shape = (C.c_int64 * max(1, w.ndim))(*w.shape)
+                _cabi.check(self._lib.l3_load_tensor(self._h, name.encode(), _cabi.f32p(w), shape, w.ndim), self._h)
+            self.finalize()
+        except Exception:
+            self.close()
+            raise
+
+    def fill_random(self, seed: int) -> None:
+        """Random weights on the device (benchmarks of shapes no checkpoint exists for), then finish the model."""
+        try:
+            _cabi.check(self._lib.l3_fill_random(self._h, int(seed)), self._h)
+            self.finalize()
+        except Exception:
+            self.close()
+            raise
+
+    def finalize(self) -> None:
+        _cabi.check(self._lib.l3_finalize(self._h), self._h)
+        self._finalized = True
+
+    def reset(self) -> None:
+        """Zero every slot's KV cache and recurrent state."""
+        _cabi.check(self._lib.l3_reset_cache(self._h), self._h)
+
+    # ---------------------------------------------------------------- forward
+    @staticmethod
+    def _ids(input_ids):
+        ids = np.asarray(input_ids)
+        if ids.ndim != 2:
+            raise ValueError(f"input_ids must be [B, L], got shape {ids.shape}")
+        if not np.issubdtype(ids.dtype, np.integer):
+            raise ValueError("input_ids must be integers")
+        return np.ascontiguousarray(ids, dtype=np.int32)
+
+    def forward(self, input_ids, start_pos: int) -> np.ndarray:
+        """`[B, L]` ids for slots 0..B-1 at `start_pos` -> float32 logits `[B, vocab]` of the last token."""
+        ids = self._ids(input_ids)
+        B, L = ids.shape
+        logits = np.empty((B, self.cfg.vocab), dtype=np.float32)
+        _cabi.check(self._lib.l3_forward(self._h, _cabi.i32p(ids), B, L, int(start_pos), _cabi.f32p(logits), None), self._h)
+        return logits
+
+    __call__ = forward
+
+    def forward_rows(self, input_ids, start_pos: int, rows, want_residual: bool = False):
+        """As `forward`, returning the logits `[len(rows), vocab]` of the chosen rows (`b * L + t`); with
+        `want_residual` also the residual stream after every layer, `[n_layers, B * L, width]`."""
+        ids = self._ids(input_ids)
+        B, L = ids.shape
+        rows = np.ascontiguousarray(np.asarray(rows, dtype=np.int32).reshape(-1))
+        logits = np.empty((len(rows), self.cfg.vocab), dtype=np.float32)
+        resid = np.empty((len(self.cfg.layers), B * L, self.cfg.width), dtype=np.float32) if want_residual else None
+        _cabi.check(self._lib.l3_forward_rows(self._h, _cabi.i32p(ids), B, L, int(start_pos),
+                                              _cabi.i32p(rows) if len(rows) else None, len(rows),
+                                              _cabi.f32p(logits) if len(rows) else None,
+                                              _cabi.f32p(resid) if want_residual else None), self._h)
+        return (logits, resid) if want_residual else logits
+
+    # ---------------------------------------------------------------- generate (greedy, the library's loop)
+    def generate(self, input_ids, max_new_tokens: int):
+        """Lazy greedy generator: prefill at position 0, then one decode step per `next()`; yields
+        `max_new_tokens` arrays `[B, 1]` int64 (the library's step function and CUDA graphs)."""
+        ids = self._ids(input_ids)
+        B, L = ids.shape
+        if max_new_tokens <= 0:
+            return
+        if L + max_new_tokens - 1 > self.cfg.max_seq_len:
+            raise ValueError(f"prompt {L} + {max_new_tokens} new tokens exceed max_seq_len {self.cfg.max_seq_len}")
+        _cabi.check(self._lib.l3_generate_begin(self._h, _cabi.i32p(ids), B, L), self._h)
+        for _ in range(max_new_tokens):
+            nxt = np.empty((B,), dtype=np.int64)
+            _cabi.check(self._lib.l3_generate_next(self._h, _cabi.i64p(nxt)), self._h)
+            yield nxt[:, None]
+
+    def generate_all(self, input_ids, max_new_tokens: int) -> np.ndarray:
+        """The whole greedy loop on the device; returns `[B, max_new_tokens]` int64."""
+        ids = self._ids(input_ids)
+        B, L = ids.shape
+        out = np.empty((B, max(0, max_new_tokens)), dtype=np.int64)
+        if max_new_tokens > 0:
+            if L + max_new_tokens - 1 > self.cfg.max_seq_len:
+                raise ValueError(f"prompt {L} + {max_new_tokens} new tokens exceed max_seq_len {self.cfg.max_seq_len}")
+            # the C entry point counts the total length (prompt included), as the reference's generate does
+            _cabi.check(self._lib.l3_generate_greedy(self._h, _cabi.i32p(ids), B, L, L + int(max_new_tokens), _cabi.i64p(out)),
+                        self._h)
+        return out
+
+    # ---------------------------------------------------------------- state inspection / measurement
+    def read_state(self, layer: int, slot: int = 0):
+        """(S [heads, dim, vdim], conv tail [channels, taps - 1] or None) of a recurrent layer's slot."""
+        l = self.cfg.layers[layer]
+        S = np.empty((l.heads, l.dim, l.vdim), dtype=np.float32)
+        tail = None
+        if l.mixer == GATED_DELTA:
+            ch = 2 * (l.kv_heads or l.heads) * l.dim + l.heads * l.vdim
+            tail = np.empty((ch, max(0, l.conv_taps - 1)), dtype=np.float32)
+        _cabi.check(self._lib.l3_read_state(self._h, layer, slot, _cabi.f32p(S), _cabi.f32p(tail) if tail is not None and tail.size else None),
+                    self._h)
+        return S, tail
+
+    def read_cache(self, layer: int):
+        """(keys, values) `[max_batch, max_seq_len, kv_heads, dim]` float32 of a softmax layer."""
+        l = self.cfg.layers[layer]
+        shape = (self.cfg.max_batch_size, self.cfg.max_seq_len, l.kv_heads or l.heads, l.dim)
+        k = np.empty(shape, dtype=np.float32)
+        v = np.empty(shape, dtype=np.float32)
+        _cabi.check(self._lib.l3_read_cache(self._h, layer, _cabi.f32p(k), _cabi.f32p(v)), self._h)
+        return k, v
+
+    def sync(self):
+        _cabi.check(self._lib.l3_sync(self._h), self._h)
+
+    def launch_count(self, reset: bool = False) -> int:
+        n = C.c_int64()
+        _cabi.check(self._lib.l3_launch_count(self._h, C.byref(n), int(reset)), self._h)
+        return n.value
+
+
+class SlotTable:
+    """Which sequence slot a live request holds.  Slots are handed out lowest-first and come back on release;
+    a released slot's state is overwritten by the next sequence that starts in it (position 0)."""
+
+    def __init__(self, n_slots: int):
+        self.free = list(range(n_slots))
+        self.slot = {}
+        self.pos = {}
+
+    def acquire(self, key) -> int:
+        if key not in self.slot:
+            if not self.free:
+                raise RuntimeError("every sequence slot is taken")
+            self.slot[key] = self.free.pop(0)
+            self.pos[key] = 0
+        return self.slot[key]
+
+    def advance(self, key, n: int) -> None:
+        self.pos[key] += n
+
+    def release(self, key) -> None:
+        if key in self.slot:
+            self.free.append(self.slot.pop(key))
+            self.free.sort()
+            self.pos.pop(key, None)

@@ -30,3 +30,33 @@ def packed_cache_path(cache_dir, digest: str, dtype: str, tp_rank: int = 0, tp_w
     import os
     kind = "bf16" if dtype in ("bfloat16", "bf16") else "f32"
     return os.path.join(os.fspath(cache_dir), f"{digest[:40]}.{kind}.tp{tp_rank}of{tp_world}.l3pack")
+
+
+def read_safetensors(path) -> dict:
+    """Tensors of a `.safetensors` file as NumPy arrays, without any library: the file is an 8-byte
+    little-endian header length, that many bytes of JSON (name -> dtype, shape, data_offsets) and the data.
+    bfloat16 comes back as float32 (exact: bf16 is the top half of an fp32), integer tables keep their type."""
+    import json
+    import struct
+    kinds = {"F32": np.float32, "F64": np.float64, "F16": np.float16, "I32": np.int32, "I64": np.int64,
+             "I16": np.int16, "I8": np.int8, "U8": np.uint8, "BOOL": np.bool_}
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n).decode("utf-8"))
+        blob = f.read()
+    out = {}
+    for name, meta in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = meta["data_offsets"]
+        shape = tuple(meta["shape"])
+        if meta["dtype"] == "BF16":
+            half = np.frombuffer(blob, dtype="<u2", count=(hi - lo) // 2, offset=lo)
+            arr = (half.astype(np.uint32) << 16).view(np.float32)
+        elif meta["dtype"] in kinds:
+            dt = np.dtype(kinds[meta["dtype"]]).newbyteorder("<")
+            arr = np.frombuffer(blob, dtype=dt, count=(hi - lo) // dt.itemsize, offset=lo)
+        else:
+            raise ValueError(f"{path}: tensor {name!r} has unsupported dtype {meta['dtype']}")
+        out[name] = arr.reshape(shape)
+    return out
