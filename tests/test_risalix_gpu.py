@@ -1,0 +1,261 @@
+"""Risalix on the GPU against the plain NumPy statement of the design (oracle/ref_risalix.py): every mixer
+alone, whole prompts against token-by-token decoding and against portions down to two tokens, batches
+against single sequences, reused slots, far keys and long decays, odd sizes, and greedy generation through
+the library's own loop.  Small random models; fp32 mode is held to 1e-4 of the logit scale, bf16 to 6e-2."""
+import numpy as np
+import pytest
+
+from oracle.ref_risalix import OracleRisalix, random_model
+
+pytestmark = pytest.mark.gpu
+
+FP32_BAR, BF16_BAR = 1e-4, 6e-2
+
+
+def attn(heads=4, kv=2, dim=16, scale=0.3, ff=0):
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": scale},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def lightning(heads=2, dim=16, vdim=16, decay=(0.7, 0.98), ff=0):
+    return {"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def delta(heads=4, kv=2, dim=16, vdim=8, conv=3, ff=0):
+    return {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "conv": conv},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def config(layers, width=64, vocab=97, side=8, mult=0.5, eps=1e-5):
+    c = {"architecture": "Risalix", "layers": layers, "norm": {"eps": eps}, "residual_mult": mult, "vocab": vocab,
+         "width": width}
+    if side:
+        c["token_side"] = {"dim": side}
+    return c
+
+
+def build(cfg, seed=0, dtype="float32", max_seq_len=128, max_batch_size=1, tensors=None):
+    from llama3_np_b200.risalix import Risalix
+    t = random_model(cfg, seed) if tensors is None else tensors
+    return Risalix(cfg, t, dtype=dtype, max_seq_len=max_seq_len, max_batch_size=max_batch_size), OracleRisalix(cfg, t)
+
+
+def err(got, want):
+    """largest row error: rms of the mean-free difference over the rms of the mean-free logits"""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    d = got - want
+    d = d - d.mean(-1, keepdims=True)
+    w = want - want.mean(-1, keepdims=True)
+    return float(np.max(np.sqrt((d * d).mean(-1)) / np.sqrt((w * w).mean())))
+
+
+def toks(n, vocab, seed=1):
+    return np.random.default_rng(seed).integers(0, vocab, n)
+
+
+ALONE = {
+    "attention": [attn(ff=0)],
+    "attention_mlp": [attn(heads=6, kv=2, dim=32, scale=0.11, ff=96)],
+    "lightning": [lightning()],
+    "lightning_wide_v": [lightning(heads=3, dim=16, vdim=32, decay=(0.5, 0.9, 0.999), ff=80)],
+    "delta": [delta()],
+    "delta_full_heads": [delta(heads=2, kv=2, dim=32, vdim=32, conv=4, ff=64)],
+}
+
+
+@pytest.mark.parametrize("name", sorted(ALONE))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_each_mixer_alone(name, dtype):
+    cfg = config(ALONE[name])
+    m, o = build(cfg, seed=3, dtype=dtype)
+    ids = toks(40, cfg["vocab"])
+    got, resid = m.forward_rows(ids[None], 0, list(range(40)), want_residual=True)
+    want = o.run(ids)
+    assert resid.shape == (1, 40, cfg["width"])
+    assert err(got, want) < (FP32_BAR if dtype == "float32" else BF16_BAR)
+    m.close()
+
+
+def test_no_side_input_and_plain_residual():
+    cfg = config([lightning(), attn(), delta()], side=0, mult=1.0)
+    m, o = build(cfg, seed=4)
+    ids = toks(24, cfg["vocab"])
+    assert err(m.forward_rows(ids[None], 0, list(range(24))), o.run(ids)) < FP32_BAR
+    m.close()
+
+
+MIXED = [lightning(ff=0), attn(ff=96), delta(ff=0), lightning(heads=4, dim=8, vdim=16, decay=(0.6, 0.9, 0.97, 0.999)), attn(heads=2, kv=1, dim=32, scale=0.2)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_then_token_by_token_and_portions(dtype):
+    cfg = config(MIXED)
+    m, o = build(cfg, seed=5, dtype=dtype, max_seq_len=160)
+    bar = FP32_BAR if dtype == "float32" else BF16_BAR
+    n = 150
+    ids = toks(n, cfg["vocab"], seed=6)
+    want = o.run(ids)
+    whole = m.forward_rows(ids[None], 0, list(range(n)))
+    assert err(whole, want) < bar
+    # every token alone, from the first one
+    one = np.stack([m.forward(ids[None, t:t + 1], t)[0] for t in range(n)])
+    assert err(one, want) < bar
+    # portions of changing size, down to two tokens and one
+    for sizes in ([37, 3, 2, 2], [2], [64, 1, 5, 2, 31]):
+        pos, i, rows = 0, 0, []
+        while pos < n:
+            c = min(sizes[i % len(sizes)], n - pos)
+            i += 1
+            rows.append(m.forward_rows(ids[None, pos:pos + c], pos, list(range(c))))
+            pos += c
+        got = np.concatenate(rows)
+        assert err(got, want) < bar
+        if dtype == "float32":  # the recurrences run the same chain however the prompt is cut
+            assert err(got, whole) < 2e-6
+    m.close()
+
+
+def test_long_decoding_matches_the_oracle():
+    cfg = config([delta(conv=4), lightning(decay=(0.9, 0.9995)), attn()], width=48)
+    m, o = build(cfg, seed=7, max_seq_len=400)
+    ids = toks(380, cfg["vocab"], seed=8)
+    want = o.run(ids)
+    m.forward_rows(ids[None, :20], 0, [])
+    got = np.stack([m.forward(ids[None, t:t + 1], t)[0] for t in range(20, 380)])
+    assert err(got, want[20:]) < FP32_BAR
+    m.close()
+
+
+def test_batch_rows_equal_single_sequences_and_slots_are_reused():
+    cfg = config(MIXED)
+    t = random_model(cfg, 9)
+    m, o = build(cfg, tensors=t, max_seq_len=64, max_batch_size=3)
+    ids = np.stack([toks(30, cfg["vocab"], seed=s) for s in (10, 11, 12)])
+    batch = m.forward_rows(ids[:, :25], 0, list(range(75)))
+    step = m.forward(ids[:, 25:26], 25)
+    for b in range(3):
+        want = o.run(ids[b, :26])
+        assert err(batch[b * 25:(b + 1) * 25], want[:25]) < FP32_BAR
+        assert err(step[b], want[25]) < FP32_BAR
+    # slot 0 held sequence 0 up to position 26; a new sequence starting there must not see any of it
+    again = m.forward_rows(ids[2:3, :30], 0, list(range(30)))
+    assert err(again, o.run(ids[2])) < FP32_BAR
+    # and continuing a slot anywhere but at its own position is refused
+    with pytest.raises(RuntimeError):
+        m.forward(ids[:1, :1], 7)
+    m.close()
+
+
+def test_far_key_dominates_attention():
+    """One early key is made to match every later query far better than the rest: its value must come through
+    hundreds of tokens later, in a prompt and in decoding."""
+    cfg = config([attn(heads=2, kv=1, dim=16, scale=4.0)], width=32, vocab=50, side=0)
+    t = random_model(cfg, 13)
+    t["l0.mix.q"] = t["l0.mix.q"] * 3.0
+    t["l0.mix.k"] = t["l0.mix.k"] * 3.0
+    m, o = build(cfg, tensors=t, max_seq_len=700)
+    ids = toks(650, 50, seed=14)
+    want = o.run(ids)
+    got = m.forward_rows(ids[None, :600], 0, list(range(600)))
+    assert err(got, want[:600]) < FP32_BAR
+    tail = np.stack([m.forward(ids[None, i:i + 1], i)[0] for i in range(600, 650)])
+    assert err(tail, want[600:]) < FP32_BAR
+    m.close()
+
+
+def test_slow_decay_remembers_the_first_token():
+    cfg = config([lightning(heads=2, dim=8, vdim=8, decay=(1.0, 0.9999))], width=32, vocab=50, side=0)
+    m, o = build(cfg, seed=15, max_seq_len=600)
+    ids = toks(520, 50, seed=16)
+    want = o.run(ids)
+    got = np.concatenate([m.forward_rows(ids[None, :500], 0, list(range(500))),
+                          np.stack([m.forward(ids[None, i:i + 1], i)[0] for i in range(500, 520)])])
+    assert err(got, want) < FP32_BAR
+    S, _ = m.read_state(0)
+    st = o.new_state()
+    for tkn in ids:
+        o.step(int(tkn), st)
+    assert np.allclose(S, st[0]["S"], rtol=2e-4, atol=2e-4)
+    m.close()
+
+
+ODD = {
+    # sizes the tiled kernels do not take, and values the usual configs make equal or 1
+    "head_24": config([attn(heads=3, kv=1, dim=24, scale=0.5, ff=50)], width=72, vocab=61, side=5),
+    "width_not_8": config([lightning(heads=1, dim=12, vdim=20, decay=(0.8,)), attn(heads=2, kv=2, dim=16, scale=1.0)], width=44, vocab=33, side=3),
+    "width_not_4": config([delta(heads=3, kv=1, dim=10, vdim=6, conv=2), attn(heads=1, kv=1, dim=48, scale=0.05)], width=30, vocab=40, side=7),
+    "one_tap_big_key": config([delta(heads=2, kv=1, dim=300, vdim=4, conv=1, ff=24)], width=40, vocab=25, side=0),
+    "many_taps": config([delta(heads=1, kv=1, dim=8, vdim=40, conv=7)], width=24, vocab=25, side=2, mult=1.0, eps=1e-3),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ODD))
+def test_odd_sizes(name):
+    cfg = ODD[name]
+    m, o = build(cfg, seed=17)
+    ids = toks(33, cfg["vocab"], seed=18)
+    want = o.run(ids)
+    got = np.concatenate([m.forward_rows(ids[None, :20], 0, list(range(20))), m.forward_rows(ids[None, 20:22], 20, [0, 1]),
+                          np.stack([m.forward(ids[None, i:i + 1], i)[0] for i in range(22, 33)])])
+    assert err(got, want) < FP32_BAR
+    m.close()
+
+
+def test_convolution_tail_and_state_after_short_portions():
+    cfg = config([delta(heads=2, kv=2, dim=8, vdim=8, conv=4)], width=32, vocab=30, side=0)
+    m, o = build(cfg, seed=19)
+    ids = toks(9, 30, seed=20)
+    for lo, hi in ((0, 1), (1, 3), (3, 4), (4, 9)):  # portions shorter than the convolution
+        m.forward_rows(ids[None, lo:hi], lo, [])
+    st = o.new_state()
+    for tkn in ids:
+        o.step(int(tkn), st)
+    S, tail = m.read_state(0)
+    want_tail = np.concatenate([st[0][f"mix.{n}.hist"] for n in "qkv"], axis=1).T  # [channels, taps - 1]
+    assert np.allclose(tail, want_tail, rtol=1e-5, atol=1e-5)
+    assert np.allclose(S, st[0]["S"], rtol=1e-4, atol=1e-5)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_library_loop(dtype):
+    cfg = config(MIXED)
+    m, o = build(cfg, seed=21, dtype=dtype, max_seq_len=96, max_batch_size=2)
+    prompts = np.stack([toks(12, cfg["vocab"], seed=s) for s in (22, 23)])
+    lazy = np.concatenate(list(m.generate(prompts, 40)), axis=1)
+    bulk = m.generate_all(prompts, 40)
+    assert np.array_equal(lazy, bulk)
+    # teacher-forced check: every emitted token is the oracle's argmax for the same prefix, unless the oracle's
+    # top two are closer than the mode's error bar
+    margin = 1e-3 if dtype == "float32" else 0.2
+    for b in range(2):
+        seq = np.concatenate([prompts[b], bulk[b]])
+        lg = o.run(seq[:-1])
+        for i in range(40):
+            row = lg[11 + i]
+            top = np.sort(row)[-2:]
+            if top[1] - top[0] > margin * np.std(row):
+                assert int(np.argmax(row)) == int(bulk[b, i]), f"sequence {b}, new token {i}"
+    m.close()
+
+
+def test_registry_and_checkpoint_folder(tmp_path):
+    import json
+    import struct
+    from llama3_np_b200.models import load_model
+    cfg = config([lightning(), attn()], width=32, vocab=41, side=4)
+    t = random_model(cfg, 24)
+    header, blob, off = {}, b"", 0
+    for k, v in t.items():
+        raw = (np.asarray(v, np.float32).view(np.uint32) >> 16).astype("<u2").tobytes()  # exact: values sit on the bf16 grid
+        header[k] = {"dtype": "BF16", "shape": list(v.shape), "data_offsets": [off, off + len(raw)]}
+        blob += raw
+        off += len(raw)
+    hj = json.dumps(header).encode()
+    (tmp_path / "model.safetensors").write_bytes(struct.pack("<Q", len(hj)) + hj + blob)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    m = load_model(str(tmp_path), dtype="float32", max_seq_len=32)
+    ids = toks(16, 41, seed=25)
+    assert err(m.forward_rows(ids[None], 0, list(range(16))), OracleRisalix(cfg, t).run(ids)) < FP32_BAR
+    m.close()
