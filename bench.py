@@ -618,6 +618,110 @@ def run_b200(a):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------ --arch risalix
+# Prefill and decode throughput of the layer-list decoder family (random weights, bf16 or fp32) at layer shapes of
+# real models, beside a Llama of the same width, head shape, feed-forward width and (to within a layer) parameter
+# count.  One JSON line; the default workload above is untouched.
+ARCH_SIZES = {"w1024": 1024, "w2048": 2048, "w4096": 4096}
+
+
+def risalix_bench_config(width, n_layers=12, vocab=32000):
+    heads = max(1, width // 128)
+    kv = max(1, heads // 4)
+    decays = [float(1.0 - 2.0 ** (-(2 + 6 * i / max(1, heads - 1)))) for i in range(heads)]
+    lin = {"type": "lightning", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "decay": decays}, "mlp": None}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5},
+           "mlp": {"kind": "dense", "ff": 4 * width}}
+    dlt = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4,
+                                              "rank_decay": width // 16, "rank_gate": width // 16}, "mlp": None}
+    pattern = [lin, att, lin, dlt, lin, att]
+    return {"architecture": "Risalix", "layers": [pattern[i % 6] for i in range(n_layers)], "norm": {"eps": 1e-5},
+            "residual_mult": 0.3, "token_side": {"dim": 256}, "vocab": vocab, "width": width}
+
+
+def risalix_layer_params(cfg):
+    W, sd, tot = cfg["width"], cfg["token_side"]["dim"], 0
+    for lc in cfg["layers"]:
+        mc = lc["mixer"]
+        H, G, dk, dv = mc["heads"], mc.get("kv_heads", mc["heads"]), mc["dim"], mc["vdim"]
+        if lc["type"] == "lightning":
+            tot += W * (2 * H * dk + 2 * H * dv) + W * H * dv
+        elif lc["type"] == "attention":
+            tot += W * (H * dk + G * dk + H) + W * H * dv
+        else:
+            tot += W * (2 * G * dk + H * dv + H + mc["rank_decay"] + mc["rank_gate"]) + mc["rank_decay"] * H * dk + mc["rank_gate"] * H * dv + W * H * dv
+        if lc["mlp"]:
+            tot += 3 * W * lc["mlp"]["ff"]
+        tot += 2 * W * sd
+    return tot
+
+
+def run_arch_compare(a):
+    import llama3_np_b200  # noqa: F401
+    from llama3_np_b200 import Llama, ModelArgs, _cabi
+    from llama3_np_b200.risalix import Risalix
+    lib = _cabi.lib()
+    hbm, tflops, how = peaks()
+    dtype = "bfloat16" if a.dtype == "bf16" else "float32"
+    wbytes = 2 if a.dtype == "bf16" else 4
+    L_pre, n_dec = a.arch_prefill, a.arch_decode
+    M = L_pre + 8
+
+    def timed_ms(m, fn, iters):
+        for _ in range(max(1, a.warmup)):
+            fn()
+        ms = C.c_float()
+        _cabi.check(lib.l3_timer_start(m._h), m._h)
+        for _ in range(iters):
+            fn()
+        _cabi.check(lib.l3_timer_stop(m._h, C.byref(ms)), m._h)
+        return ms.value / iters
+
+    def measure(m, vocab, layer_params, is_stack):
+        rng = np.random.default_rng(0)
+        rec = {}
+        ids = rng.integers(3, vocab, (1, L_pre)).astype(np.int32)
+        m.launch_count(reset=True)
+        fwd = (lambda: m.forward(ids, 0)) if is_stack else (lambda: m.forward_f32(ids, 0))
+        ms = timed_ms(m, fwd, a.steps)
+        rec["prefill"] = {"tokens": L_pre, "ms": ms, "tokens_per_s": L_pre / ms * 1e3,
+                          "tensor_frac_of_" + how: 2.0 * layer_params * L_pre / (ms / 1e3) / 1e12 / tflops}
+        for B in (1, 8):
+            p = rng.integers(3, vocab, (B, 8)).astype(np.int32)
+            gen = (lambda: m.generate_all(p, n_dec)) if is_stack else (lambda: m.generate_all(p, 8 + n_dec))
+            ms = timed_ms(m, gen, max(1, a.steps // 2))
+            step_ms = ms / n_dec
+            rec[f"decode_b{B}"] = {"new_tokens": n_dec, "ms_per_step": step_ms, "tokens_per_s": B / step_ms * 1e3,
+                                   "weight_stream_frac_of_" + how: layer_params * wbytes / (step_ms / 1e3) / 1e9 / hbm}
+        rec["gpu_launches"] = int(m.launch_count())
+        return rec
+
+    out = []
+    for name in a.arch_sizes.split(","):
+        W = ARCH_SIZES[name]
+        cfg = risalix_bench_config(W)
+        rp = risalix_layer_params(cfg)
+        heads, kv, ff = W // 128, max(1, W // 512), 4 * W
+        lp1 = W * (heads * 128 + 2 * kv * 128) + W * heads * 128 + 3 * W * ff
+        nl = max(1, round(rp / lp1))
+        clock = ClockSampler(0)
+        clock.start()
+        r = Risalix(cfg, None, dtype=dtype, max_seq_len=M, max_batch_size=8, random_seed=1)
+        rec_r = measure(r, cfg["vocab"], rp + cfg["vocab"] * W, True)
+        r.close()
+        la = ModelArgs(dim=W, n_layers=nl, n_heads=heads, n_kv_heads=kv, vocab_size=cfg["vocab"], max_seq_len=M + 8,
+                       max_batch_size=8, dtype=dtype)
+        l = Llama(None, la, hidden_dim=ff, random_seed=1)
+        rec_l = measure(l, cfg["vocab"], nl * lp1 + cfg["vocab"] * W, False)
+        l.close()
+        clk = clock.stop()
+        out.append({"size": name, "width": W, "risalix": {"layers": len(cfg["layers"]), "params_in_layers": rp, **rec_r},
+                    "llama": {"layers": nl, "params_in_layers": nl * lp1, **rec_l}, "clocks": clk})
+    print(json.dumps({"metric": "prefill / decode tokens/s, layer-list decoder (Risalix) beside Llama at equal width and size",
+                      "dtype": a.dtype, "data": "synthetic", "steps": a.steps, "warmup": a.warmup, "peak_source": how,
+                      "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops}, "sizes": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -629,7 +733,17 @@ def main():
     ap.add_argument("--total-len", type=int, default=256, help="profiling only: shorter generate")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="profiling only: skip the CPU legs")
     ap.add_argument("--no-extra", action="store_true", help="headline only: skip the `extra` / `tp` sub-records")
+    ap.add_argument("--arch", default="", choices=["", "risalix"],
+                    help="instead of the headline: prefill / decode throughput of this decoder family beside Llama at equal size")
+    ap.add_argument("--arch-sizes", default="w1024,w2048", help="comma list of " + ",".join(ARCH_SIZES))
+    ap.add_argument("--arch-prefill", type=int, default=2048)
+    ap.add_argument("--arch-decode", type=int, default=128)
     a = ap.parse_args()
+    if a.arch:
+        if a.dtype == "f32" and "--dtype" not in sys.argv:
+            a.dtype = "bf16"
+        run_arch_compare(a)
+        return
     if a.total_len != 256:
         set_total_len(a.total_len)
     if a.impl == "reference":

@@ -136,7 +136,7 @@ class OracleRisalix:
         self.t = {k: np.asarray(v, dtype=np.float64) for k, v in tensors.items()}
         self.eps = float(config["norm"]["eps"])
         self.m = float(config["residual_mult"])
-        self.sd = int(config["token_side"]["dim"])
+        self.sd = int((config.get("token_side") or {}).get("dim", 0))
         self.layers = []
         for i, lc in enumerate(config["layers"]):
             pre = f"l{i}."
@@ -154,8 +154,9 @@ class OracleRisalix:
                 assert lc["mlp"]["kind"] == "dense"
                 y = dense_ff(x, P)
                 x = x + self.m * rms_unit(y, self.eps) * (1.0 + P["norm2"])
-            e = self.t["side.embed"][token, i * self.sd:(i + 1) * self.sd]
-            x = x + self.m * side_input(x, e, P, self.eps)
+            if self.sd:
+                e = self.t["side.embed"][token, i * self.sd:(i + 1) * self.sd]
+                x = x + self.m * side_input(x, e, P, self.eps)
             if trace is not None:
                 trace.append(x.copy())
         x = rms_unit(x, self.eps) * (1.0 + self.t["final.norm"])
@@ -171,7 +172,7 @@ def random_model(config: dict, seed: int = 0, bf16_grid: bool = True):
     """Random tensors of a config, in the checkpoint's names and shapes.  `bf16_grid` rounds them to values
     that bfloat16 holds exactly, as a checkpoint would."""
     rng = np.random.default_rng(seed)
-    W, V, sd = config["width"], config["vocab"], config["token_side"]["dim"]
+    W, V, sd = config["width"], config["vocab"], (config.get("token_side") or {}).get("dim", 0)
     n = len(config["layers"])
     t = {}
 
@@ -179,7 +180,8 @@ def random_model(config: dict, seed: int = 0, bf16_grid: bool = True):
         return rng.standard_normal((o, i)) * gain / np.sqrt(i)
 
     t["embed"] = rng.standard_normal((V, W))
-    t["side.embed"] = rng.standard_normal((V, sd * n))
+    if sd:
+        t["side.embed"] = rng.standard_normal((V, sd * n))
     for i, lc in enumerate(config["layers"]):
         p, mc = f"l{i}.", lc["mixer"]
         t[p + "norm1"] = 0.1 * rng.standard_normal(W)
@@ -213,8 +215,9 @@ def random_model(config: dict, seed: int = 0, bf16_grid: bool = True):
             ff = lc["mlp"]["ff"]
             t[p + "norm2"] = 0.1 * rng.standard_normal(W)
             t[p + "mlp.gate"], t[p + "mlp.up"], t[p + "mlp.down"] = lin(ff, W), lin(ff, W), lin(W, ff)
-        t[p + "side.gate"], t[p + "side.proj"] = lin(sd, W), lin(W, sd)
-        t[p + "side.norm"] = 1.0 + 0.1 * rng.standard_normal(W)
+        if sd:
+            t[p + "side.gate"], t[p + "side.proj"] = lin(sd, W), lin(W, sd)
+            t[p + "side.norm"] = 1.0 + 0.1 * rng.standard_normal(W)
     t["final.norm"] = 0.1 * rng.standard_normal(W)
     t["head"] = lin(V, W)
     if bf16_grid:
