@@ -268,6 +268,12 @@ struct LinearArgs {
   int epi;
   EpiArgs e;
   int l2_prefetch_pairs;  // GEMV: row pairs per warp requested from L2 ahead of the dependency wait
+  // GEMV only: the input rows are x + post_mult * post_y / rms(post_y) * post_w (a post-norm residual step that has not
+  // been applied yet); the new rows also go to post_out [rows, K], a buffer other than x.  null post_y = off
+  const float* post_y;
+  const float* post_w;
+  float post_mult, post_eps;
+  float* post_out;
 };
 
 // all launchers return cudaGetLastError() of the launch

@@ -324,6 +324,7 @@ int ll_finalize(L3Model* m) {
   m->cap_tok = (int)std::max<int64_t>(m->maxB, std::min<int64_t>(want, 8192));
   const size_t ct = (size_t)m->cap_tok;
   CK(m, cudaMalloc((void**)&m->x, ct * W * 4));
+  CK(m, cudaMalloc((void**)&ll->x2, (size_t)8 * W * 4));  // second residual buffer of the fused post-norm step (<= 8 rows)
   CK(m, cudaMalloc((void**)&m->xn, ct * W * 4));  // sublayer output before its norm
   CK(m, cudaMalloc((void**)&m->q, ct * max_rq * 4));
   CK(m, cudaMalloc((void**)&m->ctx, ct * ll->max_o * 4));
@@ -393,7 +394,7 @@ void ll_destroy(L3Model* m) {
     fr(L.norm1); fr(L.norm2); fr(L.side_norm); fr(L.mix_norm); fr(L.q_norm); fr(L.k_norm); fr(L.conv_w);
     fr(L.A_log); fr(L.dt_bias); fr(L.decay); fr(L.ck); fr(L.cv); fr(L.S); fr(L.conv_tail);
   }
-  fr(ll->pin); fr(ll->aux); fr(ll->rk); fr(ll->rv); fr(ll->rg); fr(ll->rbeta); fr(ll->o); fr(ll->sg); fr(ll->sg16);
+  fr(ll->pin); fr(ll->aux); fr(ll->rk); fr(ll->rv); fr(ll->rg); fr(ll->rbeta); fr(ll->o); fr(ll->sg); fr(ll->sg16); fr(ll->x2);
   delete ll;
   m->ll = nullptr;
 }
@@ -457,15 +458,44 @@ extern "C" int l3_read_state(L3Model* m, int layer, int slot, float* S_out, floa
 }
 
 // ------------------------------------------------------------------------------ projections
+// A post-norm residual step  x += mult * y / rms(y) * w  that has been deferred: the next projection that reads x
+// through the row-streaming GEMV applies it while staging its input (linear.cu) and writes the new rows to the other
+// residual buffer; any other consumer has it applied by resid_postnorm_kernel first (ll_settle).
+struct LLPending {
+  const float* y = nullptr;
+  const float* w = nullptr;
+};
+
+static int ll_settle(L3Model* m, LLPending& pd, int rows) {
+  if (!pd.y) return L3_OK;
+  LayerList* ll = m->ll;
+  LAUNCH(m, launch_resid_postnorm(ll->xcur, pd.y, pd.w, ll->cfg.residual_mult, ll->cfg.norm_eps, rows, m->D, (bf16*)m->xn16, m->stream));
+  pd.y = nullptr;
+  return L3_OK;
+}
+
 // y = x W^T (+ epilogue).  x32: fp32 rows with stride lda (0 = K); x16: bf16 mirror with stride K, or null.
+// pd: non-null when x32 is the residual stream (ll->xcur) - a deferred step is applied on the way.
 static int ll_linear(L3Model* m, const void* W, const float* x32, const void* x16, int lda, int rows, int N, int K, int epi,
-                     const EpiArgs& e) {
+                     const EpiArgs& e, LLPending* pd = nullptr) {
+  LayerList* ll = m->ll;
   LinearArgs a{};
   a.W = W; a.x = x32; a.lda = lda; a.rows = rows; a.N = N; a.K = K; a.src_mul = 1; a.src_add = 0; a.epi = epi; a.e = e;
   const int ld = lda ? lda : K;
   if (linear_rows_supported(rows, K) && ld % 4 == 0) {
+    if (pd && pd->y) {
+      a.x = ll->xcur;
+      a.post_y = pd->y; a.post_w = pd->w; a.post_mult = ll->cfg.residual_mult; a.post_eps = ll->cfg.norm_eps; a.post_out = ll->xalt;
+      std::swap(ll->xcur, ll->xalt);
+      pd->y = nullptr;
+    } else if (pd) a.x = ll->xcur;
     LAUNCH(m, launch_linear_rows(a, m->bf16, m->bf16, m->stream));
     return L3_OK;
+  }
+  if (pd) {
+    const int rc = ll_settle(m, *pd, rows);
+    if (rc != L3_OK) return rc;
+    a.x = ll->xcur;
   }
   if (m->tc_ok && x16 && ld == K && K % 8 == 0 && K >= 64 && N >= 64) {
     TcGemmArgs t{};
@@ -492,18 +522,23 @@ static EpiArgs store_to(float* out, void* out16, int ld) {
 int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off, int B, int L, float* d_resid) {
   LayerList* ll = m->ll;
   const int ntok = B * L, W = m->D, sd = ll->cfg.side_dim;
-  const float eps = ll->cfg.norm_eps, mult = ll->cfg.residual_mult;
+  const float eps = ll->cfg.norm_eps;
   int* d_pos = m->d_scal + 0;
-  bf16* x16 = (bf16*)m->xn16;  // null in fp32 mode
+  bf16* x16 = (bf16*)m->xn16;  // null in fp32 mode; written by resid_postnorm_kernel, read by the tensor-core projections
   float* y = m->xn;
   int rc;
-  if (x16) LAUNCH(m, launch_to_bf16(m->x, (int64_t)ntok * W, x16, m->stream));
+  // the residual stream lives in xcur; a fused post-norm step (LLPending) moves it to the other buffer
+  ll->xcur = m->x;
+  ll->xalt = ll->x2;
+  LLPending pd;
+  // rows <= 8 never reach a tensor-core projection of the residual stream: no mirror needed
+  if (x16 && !linear_rows_supported(ntok, W)) LAUNCH(m, launch_to_bf16(m->x, (int64_t)ntok * W, x16, m->stream));
   for (int li = 0; li < (int)ll->layers.size(); ++li) {
     LLLayer& Ly = ll->layers[li];
     const L3LayerSpec& s = Ly.spec;
     const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim, O = H * DV;
     // every projection of the mixer's input in one GEMM
-    if ((rc = ll_linear(m, Ly.w_in, m->x, x16, 0, ntok, Ly.n_in, W, EPI_STORE, store_to(ll->pin, nullptr, Ly.n_in))) != L3_OK) return rc;
+    if ((rc = ll_linear(m, Ly.w_in, ll->xcur, x16, 0, ntok, Ly.n_in, W, EPI_STORE, store_to(ll->pin, nullptr, Ly.n_in), &pd)) != L3_OK) return rc;
     if (s.mixer == L3_MIX_SOFTMAX) {
       QkNormArgs qa{};
       qa.proj = ll->pin; qa.ld = Ly.n_in; qa.k_off = Ly.off_k; qa.wq = Ly.q_norm; qa.wk = Ly.k_norm; qa.eps = eps;
@@ -551,25 +586,27 @@ int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off,
       LAUNCH(m, launch_gated_rmsnorm(ll->o, og, O, Ly.mix_norm, DV, DV, eps, ntok, O, m->ctx, (bf16*)m->ctx16, m->stream));
     }
     if ((rc = ll_linear(m, Ly.w_o, m->ctx, m->ctx16, 0, ntok, W, O, EPI_STORE, store_to(y, nullptr, W))) != L3_OK) return rc;
-    LAUNCH(m, launch_resid_postnorm(m->x, y, Ly.norm1, mult, eps, ntok, W, x16, m->stream));
+    pd.y = y; pd.w = Ly.norm1;  // x += mult * N1(y): applied by whoever reads x next
     if (s.ff > 0) {
       EpiArgs e = store_to(m->h, m->h16, s.ff);
       e.act = ll->cfg.glu_act;
-      if ((rc = ll_linear(m, Ly.w13, m->x, x16, 0, ntok, 2 * s.ff, W, EPI_SWIGLU, e)) != L3_OK) return rc;
+      if ((rc = ll_linear(m, Ly.w13, ll->xcur, x16, 0, ntok, 2 * s.ff, W, EPI_SWIGLU, e, &pd)) != L3_OK) return rc;
       if ((rc = ll_linear(m, Ly.w2, m->h, m->h16, 0, ntok, W, s.ff, EPI_STORE, store_to(y, nullptr, W))) != L3_OK) return rc;
-      LAUNCH(m, launch_resid_postnorm(m->x, y, Ly.norm2, mult, eps, ntok, W, x16, m->stream));
+      pd.y = y; pd.w = Ly.norm2;
     }
     if (sd) {
-      if ((rc = ll_linear(m, Ly.side_gate, m->x, x16, 0, ntok, sd, W, EPI_STORE, store_to(ll->sg, nullptr, sd))) != L3_OK) return rc;
+      if ((rc = ll_linear(m, Ly.side_gate, ll->xcur, x16, 0, ntok, sd, W, EPI_STORE, store_to(ll->sg, nullptr, sd), &pd)) != L3_OK) return rc;
       LAUNCH(m, launch_side_mul(ll->sg, sd, ntok, ll->side_embed, m->bf16, (int)ll->layers.size() * sd, li * sd, d_ids, ids_ld, ids_off, L,
                                 m->cfg.vocab_size, ll->cfg.glu_act, (bf16*)ll->sg16, m->stream));
       if ((rc = ll_linear(m, Ly.side_proj, ll->sg, ll->sg16, 0, ntok, W, sd, EPI_STORE, store_to(y, nullptr, W))) != L3_OK) return rc;
-      LAUNCH(m, launch_resid_postnorm(m->x, y, Ly.side_norm, mult, eps, ntok, W, x16, m->stream));
+      pd.y = y; pd.w = Ly.side_norm;
     }
-    if (d_resid)
-      CK(m, cudaMemcpyAsync(d_resid + (size_t)li * ntok * W, m->x, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));
+    if (d_resid) {
+      if ((rc = ll_settle(m, pd, ntok)) != L3_OK) return rc;
+      CK(m, cudaMemcpyAsync(d_resid + (size_t)li * ntok * W, ll->xcur, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));
+    }
   }
-  return L3_OK;
+  return ll_settle(m, pd, ntok);  // the LM head reads ll->xcur
 }
 
 int ll_ensure_head_rows(L3Model* m, int n) {
@@ -591,6 +628,6 @@ int ll_ensure_head_rows(L3Model* m, int n) {
 
 int ll_enqueue_head(L3Model* m, int B, int L, const int32_t* d_rows, int n_rows) {
   const int rows = d_rows ? n_rows : B;
-  LAUNCH(m, launch_rmsnorm_rows(m->x, m->norm_final, m->ll->cfg.norm_eps, rows, m->D, L, L - 1, d_rows, m->xlast, (bf16*)m->xlast16, m->stream));
+  LAUNCH(m, launch_rmsnorm_rows(m->ll->xcur, m->norm_final, m->ll->cfg.norm_eps, rows, m->D, L, L - 1, d_rows, m->xlast, (bf16*)m->xlast16, m->stream));
   return ll_linear(m, m->lm_head, m->xlast, m->xlast16, 0, rows, m->VS, m->D, EPI_STORE, store_to(m->logits, nullptr, m->VS));
 }

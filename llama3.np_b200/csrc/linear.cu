@@ -61,7 +61,35 @@ __global__ void __launch_bounds__(512) linear_rows_kernel(LinearArgs a) {
   __shared__ float red_ss[32];
   for (int m = 0; m < MB; ++m) {
     float* dst = xs + (size_t)m * K;
-    if (m < a.rows) {
+    if (m < a.rows && a.post_y) {
+      // post-norm residual fused into the staging: the row this projection reads is x + mult * y / rms(y) * w, where y
+      // is the previous sublayer's output.  Every CTA rebuilds it (y and x come from L2); CTA 0 also writes it to
+      // post_out, which is NOT the buffer x lives in - the other CTAs are still reading x.
+      const float* xr = a.x + (size_t)m * K;
+      const float* yr = a.post_y + (size_t)m * K;
+      float ss = 0.f;
+      for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(yr + k);
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        *reinterpret_cast<float4*>(dst + k) = v;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) red_ss[warp] = ss;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w = 0; w < nwarp; ++w) tot += red_ss[w];
+      const float rinv = 1.0f / sqrtf(tot / (float)K + a.post_eps);
+      for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {
+        const float4 y4 = *reinterpret_cast<const float4*>(dst + k);
+        const float4 g = *reinterpret_cast<const float4*>(a.post_w + k);
+        float4 v = *reinterpret_cast<const float4*>(xr + k);
+        v.x += a.post_mult * (y4.x * rinv * g.x); v.y += a.post_mult * (y4.y * rinv * g.y);
+        v.z += a.post_mult * (y4.z * rinv * g.z); v.w += a.post_mult * (y4.w * rinv * g.w);
+        *reinterpret_cast<float4*>(dst + k) = v;
+        if (blockIdx.x == 0) *reinterpret_cast<float4*>(a.post_out + (size_t)m * K + k) = v;
+      }
+      __syncthreads();  // red_ss is reused by the next row
+    } else if (m < a.rows) {
       const float* src = a.x + (a.src_rows ? (size_t)a.src_rows[m] : (size_t)m * a.src_mul + a.src_add) * (a.lda ? a.lda : K);
       float ss = 0.f;
       for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {

@@ -13,6 +13,8 @@
 // start and written once at the end: a decode step (L = 1) moves 2 x DK x DV x 4 bytes per head and nothing
 // else of size - it is HBM-bound on the state; a prompt is a dependent chain over its tokens, the same
 // arithmetic in the same order however the prompt is cut into calls, so cutting it changes no bit.
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "common.cuh"
@@ -126,6 +128,171 @@ __global__ void __launch_bounds__(256) recur_kernel(RecurArgs a, int TPC, int CP
   }
 }
 
+
+// The same recurrences for the common shapes (256 threads: CPB * TPC = 256, R = 8, 2 <= TPC <= 32), software-pipelined:
+// while the CTA runs the TCH tokens staged in one shared-memory buffer, every thread already holds its share of the next
+// TCH tokens in registers (the global loads were issued before the compute), and stores it - through silu where asked -
+// into the other buffer afterwards.  A lane's R rows are two float4 groups (rows 4 (s + rr TPC) + 0..3), so a token costs
+// two 16-byte shared-memory loads per operand instead of eight scalar ones, without bank conflicts.  The arithmetic per
+// (column, row) and its order over the tokens are those of recur_kernel; only the order in which a column's row partials
+// are summed differs (another lane-to-row map), i.e. rounding.
+constexpr int RP_TCH = 16;
+
+template <int TPC, int MODE>
+__global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
+  constexpr int R = 8, DKP = R * TPC, CPB = 256 / TPC, TCH = RP_TCH;
+  constexpr int NA = MODE == 1 ? 3 : 2;               // staged operand arrays of DKP floats per token: q, k (, g)
+  constexpr int NPF = TCH * DKP / 256;                // floats per thread and array in the register stage
+  constexpr int NV = (TCH * CPB + 255) / 256;
+  constexpr int BUF = TCH * (NA * DKP + CPB) + TCH;   // floats per buffer: q | k | (g) | v | beta
+  extern __shared__ __align__(16) float sm[];
+  float* so = sm + 2 * BUF;                           // [TCH][CPB] outputs of the chunk
+  pdl_launch();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  constexpr int ntile_den = CPB;
+  const int ntile = (a.DV + ntile_den - 1) / ntile_den;
+  const int h = blockIdx.x / ntile, tile = blockIdx.x - h * ntile, b = blockIdx.y;
+  const int kvh = h / a.rep;
+  const int cl = tid / TPC, s = tid % TPC;
+  const int j = tile * CPB + cl;
+  const bool col_ok = j < a.DV;
+  float* Sg = a.state + ((size_t)b * a.H + h) * a.DK * a.DV;
+  float S[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = 4 * (s + (r >> 2) * TPC) + (r & 3);
+    S[r] = (col_ok && i < a.DK) ? Sg[(size_t)i * a.DV + j] : 0.f;
+  }
+  const float lam = MODE == 0 ? a.head_decay[h] : 0.f;
+  const size_t row0 = (size_t)b * a.L;
+
+  float pq[NPF], pk[NPF], pg[MODE == 1 ? NPF : 1], pv[NV], pb = 0.f;
+  auto fetch = [&](int t0) {  // global -> registers, tokens [t0, t0 + TCH) clipped to L
+#pragma unroll
+    for (int n = 0; n < NPF; ++n) {
+      const int e = tid + n * 256, tok = e / DKP, i = e % DKP;
+      const bool ok = t0 + tok < a.L && i < a.DK;
+      const size_t row = row0 + t0 + tok;
+      pq[n] = ok ? a.q[row * a.ld_q + (size_t)kvh * a.DK + i] : 0.f;
+      pk[n] = ok ? a.k[row * a.ld_k + (size_t)kvh * a.DK + i] : 0.f;
+      if (MODE == 1) pg[n] = ok ? a.g[row * ((size_t)a.H * a.DK) + (size_t)h * a.DK + i] : 0.f;
+    }
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const int e = tid + n * 256, tok = e / CPB, c = e % CPB;
+      const int jj = tile * CPB + c;
+      const bool ok = e < TCH * CPB && t0 + tok < a.L && jj < a.DV;
+      pv[n] = ok ? a.v[(row0 + t0 + tok) * a.ld_v + (size_t)h * a.DV + jj] : 0.f;
+    }
+    if (MODE == 1 && tid < TCH) pb = t0 + tid < a.L ? a.beta[(row0 + t0 + tid) * a.H + h] : 0.f;
+  };
+  auto stash = [&](float* buf) {  // registers -> shared memory (silu on the way where asked)
+#pragma unroll
+    for (int n = 0; n < NPF; ++n) {
+      const int e = tid + n * 256;
+      buf[e] = a.act_in ? silu_ref(pq[n]) : pq[n];
+      buf[TCH * DKP + e] = a.act_in ? silu_ref(pk[n]) : pk[n];
+      if (MODE == 1) buf[2 * TCH * DKP + e] = pg[n];
+    }
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const int e = tid + n * 256;
+      if (e < TCH * CPB) buf[NA * TCH * DKP + e] = a.act_in ? silu_ref(pv[n]) : pv[n];
+    }
+    if (MODE == 1 && tid < TCH) buf[TCH * (NA * DKP + CPB) + tid] = pb;
+  };
+
+  fetch(0);
+  stash(sm);
+  __syncthreads();
+  int cur = 0;
+  for (int t0 = 0; t0 < a.L; t0 += TCH, cur ^= 1) {
+    const int n = min(TCH, a.L - t0);
+    const bool more = t0 + TCH < a.L;
+    if (more) fetch(t0 + TCH);  // in flight during the compute below
+    const float* buf = sm + cur * BUF;
+    const float4* q4 = reinterpret_cast<const float4*>(buf);
+    const float4* k4 = reinterpret_cast<const float4*>(buf + TCH * DKP);
+    const float4* g4 = reinterpret_cast<const float4*>(buf + 2 * TCH * DKP);
+    const float* vb = buf + NA * TCH * DKP;
+    const float* bb = buf + TCH * (NA * DKP + CPB);
+#pragma unroll 2
+    for (int tok = 0; tok < n; ++tok) {
+      const int o4 = tok * (DKP / 4) + s;
+      const float4 ka = k4[o4], kb = k4[o4 + TPC], qa = q4[o4], qb = q4[o4 + TPC];
+      const float kr[R] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
+      const float qr[R] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+      const float vj = vb[tok * CPB + cl];
+      float acc0 = 0.f, acc1 = 0.f;
+      if (MODE == 0) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          S[r] = fmaf(lam, S[r], kr[r] * vj);
+          S[r + 4] = fmaf(lam, S[r + 4], kr[r + 4] * vj);
+          acc0 = fmaf(S[r], qr[r], acc0);
+          acc1 = fmaf(S[r + 4], qr[r + 4], acc1);
+        }
+      } else {
+        const float4 ga = g4[o4], gb = g4[o4 + TPC];
+        const float gr[R] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+        float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          S[r] *= gr[r];
+          S[r + 4] *= gr[r + 4];
+          p0 = fmaf(S[r], kr[r], p0);
+          p1 = fmaf(S[r + 4], kr[r + 4], p1);
+        }
+        float pred = p0 + p1;
+#pragma unroll
+        for (int o = TPC >> 1; o > 0; o >>= 1) pred += __shfl_xor_sync(L3_FULL, pred, o);
+        const float u = bb[tok] * (vj - pred);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          S[r] = fmaf(kr[r], u, S[r]);
+          S[r + 4] = fmaf(kr[r + 4], u, S[r + 4]);
+          acc0 = fmaf(S[r], qr[r], acc0);
+          acc1 = fmaf(S[r + 4], qr[r + 4], acc1);
+        }
+      }
+      float acc = acc0 + acc1;
+#pragma unroll
+      for (int o = TPC >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(L3_FULL, acc, o);
+      if (s == 0) so[tok * CPB + cl] = acc;
+    }
+    if (more) stash(sm + (cur ^ 1) * BUF);
+    __syncthreads();  // outputs of this chunk and the next chunk's operands are in shared memory
+    for (int e = tid; e < n * CPB; e += 256) {
+      const int tok = e / CPB, c = e % CPB;
+      const int jj = tile * CPB + c;
+      if (jj < a.DV) a.out[(row0 + t0 + tok) * ((size_t)a.H * a.DV) + (size_t)h * a.DV + jj] = so[e];
+    }
+    __syncthreads();  // the next chunk's compute writes `so` again
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = 4 * (s + (r >> 2) * TPC) + (r & 3);
+    if (col_ok && i < a.DK) Sg[(size_t)i * a.DV + j] = S[r];
+  }
+}
+
+template <int TPC>
+cudaError_t launch_recur_pipe(const RecurArgs& a, cudaStream_t s) {
+  constexpr int DKP = 8 * TPC, CPB = 256 / TPC;
+  const int NA = a.mode == 1 ? 3 : 2;
+  const size_t smem = (size_t)(2 * (RP_TCH * (NA * DKP + CPB) + RP_TCH) + RP_TCH * CPB) * sizeof(float);
+  const dim3 grid(a.H * ((a.DV + CPB - 1) / CPB), a.B);
+  auto go = [&](auto kern) {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+    }
+    return launch_k(kern, grid, dim3(256), smem, s, a);
+  };
+  return a.mode == 0 ? go(recur_pipe_kernel<TPC, 0>) : go(recur_pipe_kernel<TPC, 1>);
+}
+
 int pow2_at_least(int v) {
   int p = 1;
   while (p < v) p <<= 1;
@@ -153,6 +320,19 @@ bool recur_supported(int DK, int DV) { return DK >= 1 && DK <= 1024 && DV >= 1; 
 
 cudaError_t launch_recur(const RecurArgs& a, cudaStream_t s) {
   if (!recur_supported(a.DK, a.DV)) return cudaErrorInvalidValue;
+  static const bool pipe_on = !(getenv("L3_RECUR_PIPE") && atoi(getenv("L3_RECUR_PIPE")) == 0);
+  if (pipe_on && a.DK <= 256) {  // the pipelined kernel: its 256 threads must all own a column slice
+    const int TPC = std::min(32, pow2_at_least((a.DK + 7) / 8));
+    if (TPC >= 2 && a.DV >= 256 / TPC) {
+      switch (TPC) {
+        case 2: return launch_recur_pipe<2>(a, s);
+        case 4: return launch_recur_pipe<4>(a, s);
+        case 8: return launch_recur_pipe<8>(a, s);
+        case 16: return launch_recur_pipe<16>(a, s);
+        default: return launch_recur_pipe<32>(a, s);
+      }
+    }
+  }
   if (a.DK <= 256) return launch_recur_r<8>(a, s);
   return launch_recur_r<32>(a, s);
 }
