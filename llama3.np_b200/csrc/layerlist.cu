@@ -483,6 +483,12 @@ static int ll_linear(L3Model* m, const void* W, const float* x32, const void* x1
   a.W = W; a.x = x32; a.lda = lda; a.rows = rows; a.N = N; a.K = K; a.src_mul = 1; a.src_add = 0; a.epi = epi; a.e = e;
   const int ld = lda ? lda : K;
   if (linear_rows_supported(rows, K) && ld % 4 == 0) {
+    // the fused form costs every CTA a pass over x, y and w per row: it wins for one or two rows (0.85 -> 0.75 ms per
+    // decode step of a 12-layer width-2048 model) and loses from four rows on (8 rows: 1.87 -> 2.08 ms)
+    if (pd && pd->y && rows > 2) {
+      const int rc = ll_settle(m, *pd, rows);
+      if (rc != L3_OK) return rc;
+    }
     if (pd && pd->y) {
       a.x = ll->xcur;
       a.post_y = pd->y; a.post_w = pd->w; a.post_mult = ll->cfg.residual_mult; a.post_eps = ll->cfg.norm_eps; a.post_out = ll->xalt;
