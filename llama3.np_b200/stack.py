@@ -91,8 +91,8 @@ class StackDecoder:
             pass
 
     def load_tensors(self, tensors: Mapping[str, np.ndarray]) -> None:
-        """Upload every tensor of the mapping (checkpoint names) and finish the model.  Integer tables and other
-        names the model does not know are an error, as is a missing tensor."""
+        """Upload every tensor of the mapping (checkpoint names) and finish the model.  A tensor of the wrong shape
+        or one the model does not know is an error, as is a missing tensor."""
         try:
             for name in tensors.keys():
                 w = np.ascontiguousarray(tensors[name], dtype=np.float32)

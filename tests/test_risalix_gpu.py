@@ -259,3 +259,42 @@ def test_registry_and_checkpoint_folder(tmp_path):
     ids = toks(16, 41, seed=25)
     assert err(m.forward_rows(ids[None], 0, list(range(16))), OracleRisalix(cfg, t).run(ids)) < FP32_BAR
     m.close()
+
+
+def test_trace_runner_replays_a_trace(tmp_path):
+    """bin/trace_run as a user runs it: a checkpoint folder, steps on standard input, logits files out - two requests
+    after one another through the same slot, portions cut in odd places and longer than one forward call."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    from test_risalix_cpu import write_safetensors
+    cfg = config([lightning(), attn(ff=48), delta()], width=32, vocab=41, side=4)
+    t = random_model(cfg, 26)
+    write_safetensors(tmp_path / "model.safetensors", t)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    o = OracleRisalix(cfg, t)
+    reqs = {"a": toks(23, 41, seed=27), "b": toks(9, 41, seed=28)}
+    want = {k: o.run(v) for k, v in reqs.items()}
+    steps, expect, n = [], {}, 0
+    for rid, cuts in (("a", [11, 1, 2, 9]), ("b", [9])):
+        pos = 0
+        for c in cuts:
+            w = [0, c - 1] if c > 1 else [0]
+            steps.append({"step": n, "entries": [{"id": rid, "tokens": [int(x) for x in reqs[rid][pos:pos + c]], "want": w}],
+                          "end": [rid] if pos + c == len(reqs[rid]) else []})
+            expect[n] = want[rid][[pos + i for i in w]]
+            pos += c
+            n += 1
+    steps.append({"step": n, "entries": [], "end": []})
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "64", "--piece", "5"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(n + 1)]
+    for i, e in expect.items():
+        got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, 41)
+        assert err(got, e) < FP32_BAR, i
+    assert not (out / f"{n}.f32").exists()
