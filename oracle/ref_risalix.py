@@ -1,6 +1,6 @@
 """Plain NumPy (float64) statement of the Risalix decoder, one function per mechanism.
 
-The checker for `llama3_np_b200.risalix`: it shares no code with the product path, runs token by
+The oracle of `llama3_np_b200.risalix`: it shares no code with the product path, runs token by
 token, and keeps every intermediate in float64.  Nothing here is fast.
 
 Notation: `h` is a mixer's input row (width), `P` a dict of this layer's tensors with the
