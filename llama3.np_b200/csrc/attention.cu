@@ -583,8 +583,191 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a, int nrep)
   }
 }
 
+
+// The same attention for long prompts: 64 queries x 64 keys per tile, every thread a 4 x 4 block of scores and a
+// 4-query x (HD / 16)-dimension block of the output, so that a 16-byte shared-memory load feeds 8 FMAs instead of 3
+// (the 16-query kernel above reads one key row and four query rows per 16 FMAs and is bound by shared-memory issue).
+// Same arithmetic per score and per softmax row (fp32 throughout); a row's keys are summed in another order.
+#define PF2_ROWS 64
+#define PF2_TK 64
+#define PF2_LDS 68
+
+template <int HD, typename KVT>
+__global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nrep) {
+  constexpr int LDK = HD + 4, HD4 = HD / 4, NCH = (HD + 63) / 64;
+  extern __shared__ __align__(16) float smem[];
+  float* Qs = smem;                        // [ROWS][LDK]
+  float* Ks = Qs + PF2_ROWS * LDK;         // [TK][LDK]
+  float* Vs = Ks + PF2_TK * LDK;           // [TK][LDK]
+  float* Ss = Vs + PF2_TK * LDK;           // [ROWS][PF2_LDS]
+  float* st_m = Ss + PF2_ROWS * PF2_LDS;   // [ROWS] running max
+  float* st_l = st_m + PF2_ROWS;           // [ROWS] running sum
+  float* st_a = st_l + PF2_ROWS;           // [ROWS] rescale of this tile
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ty = tid >> 4, tx = tid & 15;
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kvh = head / nrep;
+  pdl_launch();
+  pdl_wait();
+  const int start = *a.pos_ptr;
+  const int q0 = blockIdx.x * PF2_ROWS;
+  const int nq = min(PF2_ROWS, a.L - q0);
+  const int t_hi = start + q0 + nq;
+  const float scale = attn_scale(a, HD);
+  for (int i = tid; i < PF2_ROWS * HD4; i += 256) {
+    const int r = i / HD4, d4 = i % HD4;
+    float4 v = make_float4(0, 0, 0, 0);
+    if (r < nq) v = *reinterpret_cast<const float4*>(a.q + ((size_t)(b * a.L + q0 + r) * a.HN + head) * HD + d4 * 4);
+    *reinterpret_cast<float4*>(Qs + r * LDK + d4 * 4) = v;
+  }
+  if (tid < PF2_ROWS) { st_m[tid] = -INFINITY; st_l[tid] = 0.f; st_a[tid] = 1.f; }
+  float4 acc[4][NCH];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) acc[i][c] = make_float4(0, 0, 0, 0);
+  const KVT* kbase = (const KVT*)a.cache_k + ((size_t)b * a.KVHN + kvh) * a.M * HD;
+  const KVT* vbase = (const KVT*)a.cache_v + ((size_t)b * a.KVHN + kvh) * a.M * HD;
+
+  for (int k0 = 0; k0 < t_hi; k0 += PF2_TK) {
+    __syncthreads();
+    for (int i = tid; i < PF2_TK * HD4; i += 256) {
+      const int key = i / HD4, d4 = i % HD4;
+      const int t = k0 + key;
+      float4 kv = make_float4(0, 0, 0, 0), vv = kv;
+      if (t < t_hi) {
+        kv = load_kv4<KVT>(kbase + (size_t)t * HD + d4 * 4);
+        vv = load_kv4<KVT>(vbase + (size_t)t * HD + d4 * 4);
+      }
+      *reinterpret_cast<float4*>(Ks + key * LDK + d4 * 4) = kv;
+      *reinterpret_cast<float4*>(Vs + key * LDK + d4 * 4) = vv;
+    }
+    __syncthreads();
+    {  // scores: queries ty * 4 + i, keys tx + 16 j
+      float s[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll 2
+      for (int d4 = 0; d4 < HD4; ++d4) {
+        float4 qv[4], kv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(Qs + (ty * 4 + i) * LDK + d4 * 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * j) * LDK + d4 * 4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            s[i][j] = fmaf(qv[i].x, kv[j].x, s[i][j]); s[i][j] = fmaf(qv[i].y, kv[j].y, s[i][j]);
+            s[i][j] = fmaf(qv[i].z, kv[j].z, s[i][j]); s[i][j] = fmaf(qv[i].w, kv[j].w, s[i][j]);
+          }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int key = tx + 16 * j;
+          const bool vis = (r < nq) && (k0 + key <= start + q0 + r);
+          Ss[r * PF2_LDS + key] = vis ? s[i][j] * scale : -INFINITY;
+        }
+      }
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int rr = 0; rr < 8; ++rr) {  // online softmax: warp w owns rows 8 w .. 8 w + 7
+      const int r = warp * 8 + rr;
+      const float mold = st_m[r];
+      const float s0 = Ss[r * PF2_LDS + lane], s1 = Ss[r * PF2_LDS + lane + 32];
+      const float mnew = fmaxf(mold, warp_max(fmaxf(s0, s1)));
+      float p0 = 0.f, p1 = 0.f, alpha = 1.f;
+      if (mnew > -INFINITY) {
+        p0 = expf(s0 - mnew);
+        p1 = expf(s1 - mnew);
+        alpha = expf(mold - mnew);
+      }
+      const float ps = warp_sum(p0 + p1);
+      Ss[r * PF2_LDS + lane] = p0;
+      Ss[r * PF2_LDS + lane + 32] = p1;
+      if (lane == 0) { st_l[r] = st_l[r] * alpha + ps; st_m[r] = mnew; st_a[r] = alpha; }
+    }
+    __syncthreads();
+    {  // o = o * alpha + P V: queries ty * 4 + i, dimensions tx * 4 + 64 c
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float alpha = st_a[ty * 4 + i];
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) { acc[i][c].x *= alpha; acc[i][c].y *= alpha; acc[i][c].z *= alpha; acc[i][c].w *= alpha; }
+      }
+#pragma unroll 2
+      for (int k4 = 0; k4 < PF2_TK / 4; ++k4) {
+        float4 p[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = *reinterpret_cast<const float4*>(Ss + (ty * 4 + i) * PF2_LDS + k4 * 4);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          const int d = tx * 4 + 64 * c;
+          if (d < HD) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const float4 v = *reinterpret_cast<const float4*>(Vs + (k4 * 4 + kk) * LDK + d);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float pw = kk == 0 ? p[i].x : kk == 1 ? p[i].y : kk == 2 ? p[i].z : p[i].w;
+                acc[i][c].x = fmaf(pw, v.x, acc[i][c].x); acc[i][c].y = fmaf(pw, v.y, acc[i][c].y);
+                acc[i][c].z = fmaf(pw, v.z, acc[i][c].z); acc[i][c].w = fmaf(pw, v.w, acc[i][c].w);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    if (r >= nq) continue;
+    const float inv = attn_gate(a, (size_t)(b * a.L + q0 + r), head) / st_l[r];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int d = tx * 4 + 64 * c;
+      if (d >= HD) continue;
+      float4 o = acc[i][c];
+      o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
+      const size_t oi = ((size_t)(b * a.L + q0 + r) * a.HN + head) * HD + d;
+      if (a.out_lo) {
+        float4 hi, lo;
+        split_tf32(o.x, hi.x, lo.x); split_tf32(o.y, hi.y, lo.y); split_tf32(o.z, hi.z, lo.z); split_tf32(o.w, hi.w, lo.w);
+        *reinterpret_cast<float4*>(a.out + oi) = hi;
+        *reinterpret_cast<float4*>(a.out_lo + oi) = lo;
+      } else if (a.out) *reinterpret_cast<float4*>(a.out + oi) = o;
+      if (a.out_bf16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(a.out_bf16 + oi) = pk;
+      }
+    }
+  }
+}
+
 template <int HD, typename KVT>
 static cudaError_t launch_prefill_hd(const AttnArgs& a, cudaStream_t s) {
+  static const int big_min = [] { const char* v = getenv("L3_ATTN_PF64_MIN"); return v ? atoi(v) : 48; }();
+  if (big_min > 0 && a.L >= big_min) {  // long prompts: the 64 x 64 tiling
+    auto kern = attn_prefill64_kernel<HD, KVT>;
+    const size_t smem = (size_t)(PF2_ROWS * (HD + 4) + 2 * PF2_TK * (HD + 4) + PF2_ROWS * PF2_LDS + 3 * PF2_ROWS) * sizeof(float);
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+    }
+    dim3 grid((a.L + PF2_ROWS - 1) / PF2_ROWS, a.HN, a.B);
+    return launch_k(kern, grid, dim3(256), smem, s, a, a.HN / a.KVHN);
+  }
   auto kern = attn_prefill_kernel<HD, KVT>;
   const size_t smem = (size_t)(PF_ROWS * HD + 2 * PF_TK * (HD + 4) + PF_ROWS * (PF_TK + 1) + 3 * PF_ROWS) * sizeof(float);
   if (smem > 48 * 1024) {
