@@ -610,7 +610,8 @@ __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nre
   pdl_launch();
   pdl_wait();
   const int start = *a.pos_ptr;
-  const int q0 = blockIdx.x * PF2_ROWS;
+  // the last query tile sees the most keys: it goes first, so that the long tiles do not form the tail of the launch
+  const int q0 = (gridDim.x - 1 - blockIdx.x) * PF2_ROWS;
   const int nq = min(PF2_ROWS, a.L - q0);
   const int t_hi = start + q0 + nq;
   const float scale = attn_scale(a, HD);

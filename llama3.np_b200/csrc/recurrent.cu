@@ -217,8 +217,46 @@ __global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
     const float4* g4 = reinterpret_cast<const float4*>(buf + 2 * TCH * DKP);
     const float* vb = buf + NA * TCH * DKP;
     const float* bb = buf + TCH * (NA * DKP + CPB);
+    int tok_first = 0;
+    if (MODE == 0 && TPC >= 4) {
+      // Fixed decay: nothing a token needs waits for a reduction, so four tokens' row partials are summed together -
+      // a butterfly that halves the values a lane carries at the first two levels (5 shuffles for four tokens at
+      // TPC = 16 instead of 16), after which lane s holds the complete sum of token s & 3.
+      for (; tok_first + 4 <= n; tok_first += 4) {
+        float part[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int o4 = (tok_first + u) * (DKP / 4) + s;
+          const float4 ka = k4[o4], kb = k4[o4 + TPC], qa = q4[o4], qb = q4[o4 + TPC];
+          const float kr[R] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
+          const float qr[R] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+          const float vj = vb[(tok_first + u) * CPB + cl];
+          float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            S[r] = fmaf(lam, S[r], kr[r] * vj);
+            S[r + 4] = fmaf(lam, S[r + 4], kr[r + 4] * vj);
+            a0 = fmaf(S[r], qr[r], a0);
+            a1 = fmaf(S[r + 4], qr[r + 4], a1);
+          }
+          part[u] = a0 + a1;
+        }
+        // level xor 1: lanes with bit 0 clear keep tokens 0 and 2, the others 1 and 3
+        const bool b0 = s & 1, b1 = s & 2;
+        const float send0 = b0 ? part[0] : part[1], send1 = b0 ? part[2] : part[3];
+        const float r0 = __shfl_xor_sync(L3_FULL, send0, 1), r1 = __shfl_xor_sync(L3_FULL, send1, 1);
+        const float lo = (b0 ? part[1] : part[0]) + r0;  // token (s & 1)
+        const float hi = (b0 ? part[3] : part[2]) + r1;  // token 2 + (s & 1)
+        // level xor 2: bit 1 clear keeps the low token, set keeps the high one
+        const float r2 = __shfl_xor_sync(L3_FULL, b1 ? lo : hi, 2);
+        float acc = (b1 ? hi : lo) + r2;                 // token (s & 3)
+#pragma unroll
+        for (int o = 4; o < TPC; o <<= 1) acc += __shfl_xor_sync(L3_FULL, acc, o);
+        if (s < 4) so[(tok_first + s) * CPB + cl] = acc;
+      }
+    }
 #pragma unroll 2
-    for (int tok = 0; tok < n; ++tok) {
+    for (int tok = tok_first; tok < n; ++tok) {
       const int o4 = tok * (DKP / 4) + s;
       const float4 ka = k4[o4], kb = k4[o4 + TPC], qa = q4[o4], qb = q4[o4 + TPC];
       const float kr[R] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
