@@ -567,7 +567,7 @@ int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off,
     } else if (s.mixer == L3_MIX_DECAY_LINEAR) {
       RecurArgs ra{};
       ra.mode = 0; ra.q = ll->pin + Ly.off_q; ra.k = ll->pin + Ly.off_k; ra.v = ll->pin + Ly.off_v;
-      ra.ld_q = ra.ld_k = ra.ld_v = Ly.n_in; ra.act_in = 1; ra.head_decay = Ly.decay;
+      ra.ld_q = ra.ld_k = ra.ld_v = Ly.n_in; ra.act_in = m->bf16 ? 2 : 1; ra.head_decay = Ly.decay;
       ra.state = Ly.S; ra.out = ll->o; ra.B = B; ra.L = L; ra.H = H; ra.rep = 1; ra.DK = DK; ra.DV = DV;
       LAUNCH(m, launch_recur(ra, m->stream));
       LAUNCH(m, launch_gated_rmsnorm(ll->o, ll->pin + Ly.off_g, Ly.n_in, Ly.mix_norm, O, O, eps, ntok, O, m->ctx, (bf16*)m->ctx16, m->stream));

@@ -58,7 +58,7 @@ struct RecurArgs {
                           // 1: S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q
   const float *q, *k, *v; // rows [B * L, ld_*]; head h of q / k at column (h / rep) * DK, of v at column h * DV
   int ld_q, ld_k, ld_v;
-  int act_in;             // 1: silu on q, k, v as they are read
+  int act_in;             // silu on q, k, v as they are read: 0 no, 1 exact form, 2 fast exponential and divide (pipelined kernel)
   const float* head_decay;  // mode 0: [H]
   const float* g;         // mode 1: [B * L, H * DK]
   const float* beta;      // mode 1: [B * L, H]

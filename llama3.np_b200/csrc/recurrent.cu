@@ -168,37 +168,50 @@ __global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
   const size_t row0 = (size_t)b * a.L;
 
   float pq[NPF], pk[NPF], pg[MODE == 1 ? NPF : 1], pv[NV], pb = 0.f;
+  // A thread's share of a chunk: operand element i_f of tokens tok_f, tok_f + TSTEP, ... (DKP divides 256, so i_f never
+  // changes) and value column c_f of tokens tok_v, tok_v + VSTEP, ...: the addresses advance by a constant per load.
+  constexpr int TSTEP = 256 / DKP, VSTEP = CPB >= 256 ? 1 : 256 / CPB;
+  const int i_f = tid % DKP, tok_f = tid / DKP, c_f = tid % CPB, tok_v = tid / CPB;
+  const bool i_ok = i_f < a.DK, c_ok = tile * CPB + c_f < a.DV;
+  const float* q_f = a.q + (row0 + tok_f) * a.ld_q + (size_t)kvh * a.DK + i_f;
+  const float* k_f = a.k + (row0 + tok_f) * a.ld_k + (size_t)kvh * a.DK + i_f;
+  const float* g_f = MODE == 1 ? a.g + (row0 + tok_f) * ((size_t)a.H * a.DK) + (size_t)h * a.DK + i_f : nullptr;
+  const float* v_f = a.v + (row0 + tok_v) * a.ld_v + (size_t)h * a.DV + tile * CPB + c_f;
+  const size_t q_st = (size_t)TSTEP * a.ld_q, k_st = (size_t)TSTEP * a.ld_k, g_st = (size_t)TSTEP * a.H * a.DK, v_st = (size_t)VSTEP * a.ld_v;
   auto fetch = [&](int t0) {  // global -> registers, tokens [t0, t0 + TCH) clipped to L
+    const float* qp = q_f + (size_t)t0 * a.ld_q;
+    const float* kp = k_f + (size_t)t0 * a.ld_k;
+    const float* gp = MODE == 1 ? g_f + (size_t)t0 * a.H * a.DK : nullptr;
 #pragma unroll
     for (int n = 0; n < NPF; ++n) {
-      const int e = tid + n * 256, tok = e / DKP, i = e % DKP;
-      const bool ok = t0 + tok < a.L && i < a.DK;
-      const size_t row = row0 + t0 + tok;
-      pq[n] = ok ? a.q[row * a.ld_q + (size_t)kvh * a.DK + i] : 0.f;
-      pk[n] = ok ? a.k[row * a.ld_k + (size_t)kvh * a.DK + i] : 0.f;
-      if (MODE == 1) pg[n] = ok ? a.g[row * ((size_t)a.H * a.DK) + (size_t)h * a.DK + i] : 0.f;
+      const bool ok = i_ok && t0 + tok_f + n * TSTEP < a.L;
+      pq[n] = ok ? qp[n * q_st] : 0.f;
+      pk[n] = ok ? kp[n * k_st] : 0.f;
+      if (MODE == 1) pg[n] = ok ? gp[n * g_st] : 0.f;
     }
+    const float* vp = v_f + (size_t)t0 * a.ld_v;
 #pragma unroll
     for (int n = 0; n < NV; ++n) {
-      const int e = tid + n * 256, tok = e / CPB, c = e % CPB;
-      const int jj = tile * CPB + c;
-      const bool ok = e < TCH * CPB && t0 + tok < a.L && jj < a.DV;
-      pv[n] = ok ? a.v[(row0 + t0 + tok) * a.ld_v + (size_t)h * a.DV + jj] : 0.f;
+      const bool ok = c_ok && tok_v + n * VSTEP < TCH && t0 + tok_v + n * VSTEP < a.L;
+      pv[n] = ok ? vp[n * v_st] : 0.f;
     }
     if (MODE == 1 && tid < TCH) pb = t0 + tid < a.L ? a.beta[(row0 + t0 + tid) * a.H + h] : 0.f;
   };
+  // silu of the staged operands: the exact form in fp32 mode (act_in 1), exp2-based with a fast divide where the
+  // operands are bf16-rounded projections anyway (act_in 2)
+  auto act = [&](float x) { return a.act_in == 2 ? __fdividef(x, 1.0f + __expf(-x)) : silu_ref(x); };
   auto stash = [&](float* buf) {  // registers -> shared memory (silu on the way where asked)
 #pragma unroll
     for (int n = 0; n < NPF; ++n) {
       const int e = tid + n * 256;
-      buf[e] = a.act_in ? silu_ref(pq[n]) : pq[n];
-      buf[TCH * DKP + e] = a.act_in ? silu_ref(pk[n]) : pk[n];
+      buf[e] = a.act_in ? act(pq[n]) : pq[n];
+      buf[TCH * DKP + e] = a.act_in ? act(pk[n]) : pk[n];
       if (MODE == 1) buf[2 * TCH * DKP + e] = pg[n];
     }
 #pragma unroll
     for (int n = 0; n < NV; ++n) {
       const int e = tid + n * 256;
-      if (e < TCH * CPB) buf[NA * TCH * DKP + e] = a.act_in ? silu_ref(pv[n]) : pv[n];
+      if (e < TCH * CPB) buf[NA * TCH * DKP + e] = a.act_in ? act(pv[n]) : pv[n];
     }
     if (MODE == 1 && tid < TCH) buf[TCH * (NA * DKP + CPB) + tid] = pb;
   };
