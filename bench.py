@@ -634,9 +634,9 @@ def risalix_bench_config(width, n_layers=12, vocab=32000):
            "mlp": {"kind": "dense", "ff": 4 * width}}
     dlt = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4,
                                               "rank_decay": width // 16, "rank_gate": width // 16}, "mlp": None}
-    pattern = [lin, att, lin, dlt, lin, att]
+    pattern = [lin, dlt, lin, att, lin, att]
     return {"architecture": "Risalix", "layers": [pattern[i % 6] for i in range(n_layers)], "norm": {"eps": 1e-5},
-            "residual_mult": 0.3, "token_side": {"dim": 256}, "vocab": vocab, "width": width}
+            "residual_mult": 0.5, "token_side": {"dim": 256}, "vocab": vocab, "width": width}
 
 
 def risalix_layer_params(cfg):

@@ -43,7 +43,10 @@ def stack_config(config: Mapping, shapes: Optional[Mapping[str, tuple]] = None, 
         if kind == "attention":
             spec.scale = float(mc["scale"])
         elif kind == "lightning":
-            spec.decay = [float(x) for x in mc["decay"]]
+            d = mc["decay"]  # one value per head; a single number serves every head
+            spec.decay = [float(x) for x in d] if isinstance(d, (list, tuple)) else [float(d)] * spec.heads
+            if len(spec.decay) != spec.heads:
+                raise ValueError(f"layer {i}: {len(spec.decay)} decays for {spec.heads} heads")
         else:
             spec.conv_taps = int(mc["conv"])
             if shapes is not None:

@@ -60,6 +60,15 @@ def test_config_reader_takes_every_size_from_config_or_shapes():
     assert (dlt.mixer, dlt.heads, dlt.kv_heads, dlt.conv_taps, dlt.ff) == (GATED_DELTA, 4, 2, 3, 24)
     assert dlt.rank_decay == t["l1.mix.a1"].shape[0] and dlt.rank_gate == t["l1.mix.g1"].shape[0]
     assert (att.mixer, att.heads, att.kv_heads, att.dim, att.scale) == (SOFTMAX, 6, 2, 8, pytest.approx(0.2))
+    one = json.loads(json.dumps(CFG))
+    one["layers"][0]["mixer"]["decay"] = 0.9  # a single number serves every head
+    del one["token_side"]
+    sc1 = stack_config(one, {k: v.shape for k, v in t.items()})
+    assert list(sc1.layers[0].decay) == [0.9, 0.9] and sc1.side_dim == 0
+    bad = json.loads(json.dumps(CFG))
+    bad["layers"][0]["mixer"]["decay"] = [0.5]
+    with pytest.raises(ValueError):
+        stack_config(bad, None)
     bad = json.loads(json.dumps(CFG))
     bad["layers"][0]["type"] = "hyena"
     with pytest.raises(ValueError):

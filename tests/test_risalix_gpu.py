@@ -298,3 +298,27 @@ def test_trace_runner_replays_a_trace(tmp_path):
         got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, 41)
         assert err(got, e) < FP32_BAR, i
     assert not (out / f"{n}.f32").exists()
+
+
+def test_generate_command_prints_the_loop_s_tokens(tmp_path):
+    """bin/generate on a checkpoint folder: two prompts from a file as one batch, the printed ids are the ones the
+    model's own greedy loop gives in-process."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    from llama3_np_b200.models import load_model
+    from test_risalix_cpu import write_safetensors
+    cfg = config([delta(heads=2, kv=1), attn(ff=40), lightning()], width=32, vocab=47, side=4)
+    write_safetensors(tmp_path / "model.safetensors", random_model(cfg, 29))
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    prompts = np.stack([toks(7, 47, seed=s) for s in (30, 31)])
+    (tmp_path / "prompts.txt").write_text("\n".join(" ".join(str(int(x)) for x in p) for p in prompts) + "\n")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), "--model", str(tmp_path), "--dtype", "float32",
+                        "--batch-file", str(tmp_path / "prompts.txt"), "--new", "12"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    printed = np.array([[int(x) for x in line.split()] for line in r.stdout.strip().splitlines()[-2:]])
+    m = load_model(str(tmp_path), dtype="float32", max_seq_len=19, max_batch_size=2)
+    assert np.array_equal(printed, m.generate_all(prompts, 12))
+    m.close()
