@@ -339,6 +339,10 @@ int ll_finalize(L3Model* m) {
   CK(m, cudaMalloc((void**)&ll->rbeta, ct * max_h * 4));
   CK(m, cudaMalloc((void**)&ll->o, ct * ll->max_o * 4));
   CK(m, cudaMalloc((void**)&ll->sg, ct * std::max(1, sd) * 4));
+  for (const LLLayer& L : ll->layers)
+    if (L.spec.mixer == L3_MIX_DECAY_LINEAR && recur_chunk_shape(L.spec.dim, L.spec.vdim) && ct >= 128)
+      ll->chunk_ws_floats = std::max(ll->chunk_ws_floats, (ct / 64 + m->maxB) * (size_t)L.spec.heads * L.spec.dim * L.spec.vdim);
+  if (ll->chunk_ws_floats) CK(m, cudaMalloc((void**)&ll->chunk_ws, ll->chunk_ws_floats * 4));
   // tensor cores: bf16 mode only.  fp32 mode is the exact mode of this family: every product is an fp32 FFMA chain
   // (the 3xTF32 scheme of the Llama path would need a (hi, lo) copy of the residual stream beside the stream itself).
   m->tc_ok = m->bf16 && !(m->cfg.flags & L3_FLAG_NO_TENSORCORE) && tc_gemm_supported(W);
@@ -394,7 +398,7 @@ void ll_destroy(L3Model* m) {
     fr(L.norm1); fr(L.norm2); fr(L.side_norm); fr(L.mix_norm); fr(L.q_norm); fr(L.k_norm); fr(L.conv_w);
     fr(L.A_log); fr(L.dt_bias); fr(L.decay); fr(L.ck); fr(L.cv); fr(L.S); fr(L.conv_tail);
   }
-  fr(ll->pin); fr(ll->aux); fr(ll->rk); fr(ll->rv); fr(ll->rg); fr(ll->rbeta); fr(ll->o); fr(ll->sg); fr(ll->sg16); fr(ll->x2);
+  fr(ll->pin); fr(ll->aux); fr(ll->rk); fr(ll->rv); fr(ll->rg); fr(ll->rbeta); fr(ll->o); fr(ll->sg); fr(ll->sg16); fr(ll->x2); fr(ll->chunk_ws);
   delete ll;
   m->ll = nullptr;
 }
@@ -569,6 +573,7 @@ int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off,
       ra.mode = 0; ra.q = ll->pin + Ly.off_q; ra.k = ll->pin + Ly.off_k; ra.v = ll->pin + Ly.off_v;
       ra.ld_q = ra.ld_k = ra.ld_v = Ly.n_in; ra.act_in = m->bf16 ? 2 : 1; ra.head_decay = Ly.decay;
       ra.state = Ly.S; ra.out = ll->o; ra.B = B; ra.L = L; ra.H = H; ra.rep = 1; ra.DK = DK; ra.DV = DV;
+      ra.ws = ll->chunk_ws; ra.ws_floats = ll->chunk_ws_floats;
       LAUNCH(m, launch_recur(ra, m->stream));
       LAUNCH(m, launch_gated_rmsnorm(ll->o, ll->pin + Ly.off_g, Ly.n_in, Ly.mix_norm, O, O, eps, ntok, O, m->ctx, (bf16*)m->ctx16, m->stream));
     } else {

@@ -44,6 +44,8 @@ struct LayerList {
   // workspace beyond the shared buffers of L3Model (x, xn = sublayer output, q, ctx, h + bf16 mirrors)
   float *pin = nullptr, *aux = nullptr, *rk = nullptr, *rv = nullptr, *rg = nullptr, *rbeta = nullptr, *o = nullptr;
   float* sg = nullptr;
+  float* chunk_ws = nullptr;               // chunk states of the chunk-parallel decay-linear recurrence (prompts)
+  size_t chunk_ws_floats = 0;
   float* x2 = nullptr;                     // second residual buffer, 8 rows (fused post-norm step of the GEMV path)
   float *xcur = nullptr, *xalt = nullptr;  // where the residual stream of the running step lives / the other buffer
   void* sg16 = nullptr;

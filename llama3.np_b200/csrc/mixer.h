@@ -65,9 +65,16 @@ struct RecurArgs {
   float* state;           // [maxB, H, DK, DV]
   float* out;             // [B * L, H * DV]
   int B, L, H, rep, DK, DV;
+  float* ws;              // mode 0, may be null: room for one state matrix per (sequence, head, chunk of 64 tokens);
+  size_t ws_floats;       // with it, prompts of the common shapes run in the chunk-parallel form (recur_chunk.cu)
 };
 bool recur_supported(int DK, int DV);
 cudaError_t launch_recur(const RecurArgs& a, cudaStream_t s);
+// chunk-parallel form of mode 0 (recur_chunk.cu): floats of workspace a call needs, whether a call can take it, the launch
+size_t recur_chunk_ws_floats(int B, int L, int H, int DK, int DV);
+bool recur_chunk_shape(int DK, int DV);
+bool recur_chunk_supported(const RecurArgs& a);
+cudaError_t launch_recur_chunk(const RecurArgs& a, cudaStream_t s);
 
 // ---- attention for head sizes the tiled kernels do not take (attn_any.cu): same arguments, any HD
 cudaError_t launch_attn_any(const AttnArgs& a, bool kv_bf16, cudaStream_t s);

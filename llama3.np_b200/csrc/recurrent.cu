@@ -371,6 +371,8 @@ bool recur_supported(int DK, int DV) { return DK >= 1 && DK <= 1024 && DV >= 1; 
 
 cudaError_t launch_recur(const RecurArgs& a, cudaStream_t s) {
   if (!recur_supported(a.DK, a.DV)) return cudaErrorInvalidValue;
+  static const bool chunk_on = !(getenv("L3_RECUR_CHUNK") && atoi(getenv("L3_RECUR_CHUNK")) == 0);
+  if (chunk_on && recur_chunk_supported(a)) return launch_recur_chunk(a, s);  // prompts of the common shapes
   static const bool pipe_on = !(getenv("L3_RECUR_PIPE") && atoi(getenv("L3_RECUR_PIPE")) == 0);
   if (pipe_on && a.DK <= 256) {  // the pipelined kernel: its 256 threads must all own a column slice
     const int TPC = std::min(32, pow2_at_least((a.DK + 7) / 8));

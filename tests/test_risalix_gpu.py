@@ -322,3 +322,34 @@ def test_generate_command_prints_the_loop_s_tokens(tmp_path):
     m = load_model(str(tmp_path), dtype="float32", max_seq_len=19, max_batch_size=2)
     assert np.array_equal(printed, m.generate_all(prompts, 12))
     m.close()
+
+
+@pytest.mark.parametrize("dim,vdim", [(64, 64), (128, 192), (64, 128)])
+def test_long_prompts_of_decay_linear_layers_run_chunk_parallel(dim, vdim):
+    """Prompts of 128 tokens and more take the chunk-parallel form of the fixed-decay recurrence for key sizes 64 / 128:
+    against the token-by-token oracle with a last chunk that is not full, a portion that continues from a state,
+    a fast and a very slow decay, two sequences of a batch, and decoding from the state it leaves."""
+    cfg = config([lightning(heads=2, dim=dim, vdim=vdim, decay=(0.35, 0.9997), ff=0), attn(), lightning(heads=1, dim=dim, vdim=vdim, decay=(0.93,))],
+                 width=64, vocab=59, side=0)
+    t = random_model(cfg, 33)
+    m, o = build(cfg, tensors=t, max_seq_len=520, max_batch_size=2)
+    ids = np.stack([toks(500, 59, seed=s) for s in (34, 35)])
+    want = [o.run(ids[b]) for b in range(2)]
+    # 301 tokens (4 full chunks + 45), then 150 more from that state (chunked again), then short portions and single tokens
+    got = [m.forward_rows(ids[:, :301], 0, list(range(2 * 301))).reshape(2, 301, -1),
+           m.forward_rows(ids[:, 301:451], 301, list(range(2 * 150))).reshape(2, 150, -1),
+           m.forward_rows(ids[:, 451:480], 451, list(range(2 * 29))).reshape(2, 29, -1)]
+    got += [m.forward(ids[:, i:i + 1], i)[:, None, :] for i in range(480, 500)]
+    got = np.concatenate(got, axis=1)
+    for b in range(2):
+        assert err(got[b], want[b]) < FP32_BAR
+    S, _ = m.read_state(0, slot=1)
+    st = o.new_state()
+    for tkn in ids[1]:
+        o.step(int(tkn), st)
+    assert np.abs(S - st[0]["S"]).max() < 2e-5 * np.abs(st[0]["S"]).max()  # the slow head's state grows to hundreds
+    # the same prompt token by token (the sequential kernel) gives the same logits to fp32 rounding
+    one = m.forward_rows(ids[:1, :127], 0, list(range(127)))
+    one = np.concatenate([one, m.forward_rows(ids[:1, 127:254], 127, list(range(127)))])
+    assert err(one, got[0, :254]) < 2e-5
+    m.close()
