@@ -590,19 +590,23 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a, int nrep)
 // Same arithmetic per score and per softmax row (fp32 throughout); a row's keys are summed in another order.
 #define PF2_ROWS 64
 #define PF2_TK 64
-#define PF2_LDS 68
+#define PF2_LDS 64
 
 template <int HD, typename KVT>
 __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nrep) {
   constexpr int LDK = HD + 4, HD4 = HD / 4, NCH = (HD + 63) / 64;
   extern __shared__ __align__(16) float smem[];
-  float* Qs = smem;                        // [ROWS][LDK]
-  float* Ks = Qs + PF2_ROWS * LDK;         // [TK][LDK]
-  float* Vs = Ks + PF2_TK * LDK;           // [TK][LDK]
-  float* Ss = Vs + PF2_TK * LDK;           // [ROWS][PF2_LDS]
-  float* st_m = Ss + PF2_ROWS * PF2_LDS;   // [ROWS] running max
-  float* st_l = st_m + PF2_ROWS;           // [ROWS] running sum
-  float* st_a = st_l + PF2_ROWS;           // [ROWS] rescale of this tile
+  // 64 * (4 HD + 68) floats: 115712 bytes at HD = 128, so that two CTAs share an SM.  Only the key tile is padded (its
+  // rows are read by adjacent lanes).  Q and the score tile are read by the two half-warps of a warp at rows 4 apart:
+  // their 16-byte slots are swapped pairwise in every other group of 4 rows (slot ^ (row / 4 & 1)), which keeps the
+  // two reads in different banks without padding.  The softmax state sits in the key tile's padding columns.
+  float* Qs = smem;                        // [ROWS][HD], slots swizzled
+  float* Ks = Qs + PF2_ROWS * HD;          // [TK][LDK]; row r, columns HD .. HD + 2: running max, running sum, rescale
+  float* Vs = Ks + PF2_TK * LDK;           // [TK][HD]
+  float* Ss = Vs + PF2_TK * HD;            // [ROWS][PF2_LDS], slots swizzled
+#define ST_M(r) Ks[(r) * LDK + HD]
+#define ST_L(r) Ks[(r) * LDK + HD + 1]
+#define ST_A(r) Ks[(r) * LDK + HD + 2]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int ty = tid >> 4, tx = tid & 15;
   const int head = blockIdx.y, b = blockIdx.z;
@@ -619,9 +623,9 @@ __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nre
     const int r = i / HD4, d4 = i % HD4;
     float4 v = make_float4(0, 0, 0, 0);
     if (r < nq) v = *reinterpret_cast<const float4*>(a.q + ((size_t)(b * a.L + q0 + r) * a.HN + head) * HD + d4 * 4);
-    *reinterpret_cast<float4*>(Qs + r * LDK + d4 * 4) = v;
+    *reinterpret_cast<float4*>(Qs + r * HD + ((d4 ^ ((r >> 2) & 1)) * 4)) = v;
   }
-  if (tid < PF2_ROWS) { st_m[tid] = -INFINITY; st_l[tid] = 0.f; st_a[tid] = 1.f; }
+  if (tid < PF2_ROWS) { ST_M(tid) = -INFINITY; ST_L(tid) = 0.f; ST_A(tid) = 1.f; }
   float4 acc[4][NCH];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -641,7 +645,7 @@ __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nre
         vv = load_kv4<KVT>(vbase + (size_t)t * HD + d4 * 4);
       }
       *reinterpret_cast<float4*>(Ks + key * LDK + d4 * 4) = kv;
-      *reinterpret_cast<float4*>(Vs + key * LDK + d4 * 4) = vv;
+      *reinterpret_cast<float4*>(Vs + key * HD + d4 * 4) = vv;
     }
     __syncthreads();
     {  // scores: queries ty * 4 + i, keys tx + 16 j
@@ -654,7 +658,7 @@ __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nre
       for (int d4 = 0; d4 < HD4; ++d4) {
         float4 qv[4], kv[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(Qs + (ty * 4 + i) * LDK + d4 * 4);
+        for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(Qs + (ty * 4 + i) * HD + ((d4 ^ (ty & 1)) * 4));
 #pragma unroll
         for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * j) * LDK + d4 * 4);
 #pragma unroll
@@ -672,7 +676,7 @@ __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nre
         for (int j = 0; j < 4; ++j) {
           const int key = tx + 16 * j;
           const bool vis = (r < nq) && (k0 + key <= start + q0 + r);
-          Ss[r * PF2_LDS + key] = vis ? s[i][j] * scale : -INFINITY;
+          Ss[r * PF2_LDS + (key ^ ((ty & 1) << 2))] = vis ? s[i][j] * scale : -INFINITY;
         }
       }
     }
@@ -680,7 +684,7 @@ __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nre
 #pragma unroll 2
     for (int rr = 0; rr < 8; ++rr) {  // online softmax: warp w owns rows 8 w .. 8 w + 7
       const int r = warp * 8 + rr;
-      const float mold = st_m[r];
+      const float mold = ST_M(r);
       const float s0 = Ss[r * PF2_LDS + lane], s1 = Ss[r * PF2_LDS + lane + 32];
       const float mnew = fmaxf(mold, warp_max(fmaxf(s0, s1)));
       float p0 = 0.f, p1 = 0.f, alpha = 1.f;
@@ -692,13 +696,13 @@ __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nre
       const float ps = warp_sum(p0 + p1);
       Ss[r * PF2_LDS + lane] = p0;
       Ss[r * PF2_LDS + lane + 32] = p1;
-      if (lane == 0) { st_l[r] = st_l[r] * alpha + ps; st_m[r] = mnew; st_a[r] = alpha; }
+      if (lane == 0) { ST_L(r) = ST_L(r) * alpha + ps; ST_M(r) = mnew; ST_A(r) = alpha; }
     }
     __syncthreads();
     {  // o = o * alpha + P V: queries ty * 4 + i, dimensions tx * 4 + 64 c
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float alpha = st_a[ty * 4 + i];
+        const float alpha = ST_A(ty * 4 + i);
 #pragma unroll
         for (int c = 0; c < NCH; ++c) { acc[i][c].x *= alpha; acc[i][c].y *= alpha; acc[i][c].z *= alpha; acc[i][c].w *= alpha; }
       }
@@ -706,14 +710,14 @@ __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nre
       for (int k4 = 0; k4 < PF2_TK / 4; ++k4) {
         float4 p[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) p[i] = *reinterpret_cast<const float4*>(Ss + (ty * 4 + i) * PF2_LDS + k4 * 4);
+        for (int i = 0; i < 4; ++i) p[i] = *reinterpret_cast<const float4*>(Ss + (ty * 4 + i) * PF2_LDS + ((k4 ^ (ty & 1)) * 4));
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
           const int d = tx * 4 + 64 * c;
           if (d < HD) {
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-              const float4 v = *reinterpret_cast<const float4*>(Vs + (k4 * 4 + kk) * LDK + d);
+              const float4 v = *reinterpret_cast<const float4*>(Vs + (k4 * 4 + kk) * HD + d);
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 const float pw = kk == 0 ? p[i].x : kk == 1 ? p[i].y : kk == 2 ? p[i].z : p[i].w;
@@ -731,7 +735,7 @@ __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nre
   for (int i = 0; i < 4; ++i) {
     const int r = ty * 4 + i;
     if (r >= nq) continue;
-    const float inv = attn_gate(a, (size_t)(b * a.L + q0 + r), head) / st_l[r];
+    const float inv = attn_gate(a, (size_t)(b * a.L + q0 + r), head) / ST_L(r);
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
       const int d = tx * 4 + 64 * c;
@@ -756,12 +760,16 @@ __global__ void __launch_bounds__(256) attn_prefill64_kernel(AttnArgs a, int nre
   }
 }
 
+#undef ST_M
+#undef ST_L
+#undef ST_A
+
 template <int HD, typename KVT>
 static cudaError_t launch_prefill_hd(const AttnArgs& a, cudaStream_t s) {
   static const int big_min = [] { const char* v = getenv("L3_ATTN_PF64_MIN"); return v ? atoi(v) : 48; }();
   if (big_min > 0 && a.L >= big_min) {  // long prompts: the 64 x 64 tiling
     auto kern = attn_prefill64_kernel<HD, KVT>;
-    const size_t smem = (size_t)(PF2_ROWS * (HD + 4) + 2 * PF2_TK * (HD + 4) + PF2_ROWS * PF2_LDS + 3 * PF2_ROWS) * sizeof(float);
+    const size_t smem = (size_t)(PF2_ROWS * HD + PF2_TK * (HD + 4) + PF2_TK * HD + PF2_ROWS * PF2_LDS) * sizeof(float);
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
