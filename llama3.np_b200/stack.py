@@ -183,6 +183,29 @@ class StackDecoder:
                         self._h)
         return out
 
+    def generate_ragged(self, prompts, max_new_tokens: int, eos_id: Optional[int] = None):
+        """Greedy generation for prompts of different lengths: a list with `max_new_tokens` new ids per prompt (cut
+        after the first `eos_id`, if given).  The recurrent layers take one length per call, so the scheduler here is
+        length bucketing on the host: prompts of one length share a batch (at most `max_batch_size` of them), the
+        buckets run one after another through `generate_all`, and every prompt yields what it yields alone."""
+        seqs = [np.ascontiguousarray(np.asarray(p).reshape(-1), dtype=np.int32) for p in prompts]
+        if not seqs or any(len(p) == 0 for p in seqs):
+            raise ValueError("need at least one non-empty prompt")
+        buckets = {}
+        for i, p in enumerate(seqs):
+            buckets.setdefault(len(p), []).append(i)
+        out = [None] * len(seqs)
+        for length in sorted(buckets):
+            idx = buckets[length]
+            for lo in range(0, len(idx), self.cfg.max_batch_size):
+                part = idx[lo:lo + self.cfg.max_batch_size]
+                toks = self.generate_all(np.stack([seqs[i] for i in part]), max_new_tokens)
+                for row, i in zip(toks, part):
+                    if eos_id is not None and (row == eos_id).any():
+                        row = row[: int(np.argmax(row == eos_id)) + 1]
+                    out[i] = row.copy()
+        return out
+
     # ---------------------------------------------------------------- state inspection / measurement
     def read_state(self, layer: int, slot: int = 0):
         """(S [heads, dim, vdim], conv tail [channels, taps - 1] or None) of a recurrent layer's slot."""

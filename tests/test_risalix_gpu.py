@@ -353,3 +353,24 @@ def test_long_prompts_of_decay_linear_layers_run_chunk_parallel(dim, vdim):
     one = np.concatenate([one, m.forward_rows(ids[:1, 127:254], 127, list(range(127)))])
     assert err(one, got[0, :254]) < 2e-5
     m.close()
+
+
+def test_unequal_prompts_are_bucketed_by_length_and_match_each_alone():
+    """`generate_ragged`: five prompts of three lengths with two sequence slots - buckets of one length, split where a
+    bucket is larger than the batch; every prompt yields what it yields alone, in the caller's order, and stops at EOS."""
+    cfg = config(MIXED)
+    t = random_model(cfg, 36)
+    m, _ = build(cfg, tensors=t, max_seq_len=64, max_batch_size=2)
+    lens = [9, 4, 9, 17, 9]
+    prompts = [toks(n, cfg["vocab"], seed=40 + i) for i, n in enumerate(lens)]
+    got = m.generate_ragged(prompts, 14)
+    assert [len(g) for g in got] == [14] * 5
+    for p, g in zip(prompts, got):
+        assert np.array_equal(g, m.generate_all(p[None], 14)[0])
+    eos = int(got[3][5])
+    cut = m.generate_ragged(prompts, 14, eos_id=eos)
+    first = int(np.argmax(got[3] == eos))
+    assert np.array_equal(cut[3], got[3][: first + 1])
+    with pytest.raises(ValueError):
+        m.generate_ragged([prompts[0], []], 3)
+    m.close()
