@@ -143,6 +143,14 @@ int l3_generate_ragged(L3Model* m, const int32_t* ids, const int32_t* lens, int 
 #define L3_MIX_DECAY_LINEAR 1  /* linear attention, one fixed decay per head: S <- decay S + k v^T, o = S^T q */
 #define L3_MIX_GATED_DELTA 2   /* gated delta rule, one data-dependent decay per head and key channel,
                                   short causal convolutions on q, k, v                                       */
+#define L3_MIX_LATENT 3        /* causal softmax attention over ONE cached latent row per token: queries through a
+                                  normed latent of width q_rank; the cache row is [normed latent (kv_rank) | rotated key
+                                  part (rot_dim)] shared by all heads; per-head keys / values are expanded from the latent
+                                  (here: folded into the query and the output); rotary pairs (2i, 2i + 1) on the first
+                                  rot_dims entries of the rotated part; sigmoid gate per head                          */
+#define L3_MIX_MINGRU 4        /* element-wise gated recurrence of width dim (heads = vdim = 1):
+                                  S <- (1 - z) S + z c,  z = sigmoid(Wz h + bz),  c = u + 1/2 (u >= 0) | sigmoid(u),
+                                  u = Wx h + bx;  output Wo (S * silu(Wg h))                                            */
 typedef struct L3LayerSpec {
   int32_t mixer;        /* L3_MIX_* */
   int32_t heads;        /* value heads (query heads for L3_MIX_SOFTMAX) */
@@ -155,6 +163,16 @@ typedef struct L3LayerSpec {
   int32_t ff;           /* width of the gated feed-forward; 0 = the layer has none */
   float scale;          /* L3_MIX_SOFTMAX: multiplier of q . k */
   const float* decay;   /* L3_MIX_DECAY_LINEAR: [heads] decays (host memory, copied by l3_create_stack) */
+  /* L3_MIX_LATENT: dim = un-rotated query / key size per head, vdim = value size per head */
+  int32_t q_rank, kv_rank;   /* widths of the query latent and of the cached key / value latent */
+  int32_t rot_dim, rot_dims; /* rotated query / key size per head; how many of its leading entries rotate (even) */
+  double rot_base;           /* pair i turns by position * rot_base^(-2 i / rot_dims) */
+  /* feed-forward as a mixture of experts (experts > 0; ff is then one expert's width):
+   * expert e = down_e relu(up_e x)^2; the router scores experts + identity slots with a softmax, picks `top` of them by
+   * score + correction inside the `groups_keep` best of `groups` equal groups of neighbours, and weighs the picked
+   * ones by router_scale * score (not renormalised); an identity slot returns its input */
+  int32_t experts, top, identity, groups, groups_keep;
+  float router_scale;
 } L3LayerSpec;
 
 typedef struct L3StackConfig {
@@ -166,6 +184,15 @@ typedef struct L3StackConfig {
   int32_t norm_one_plus; /* 1: the layer norms and the final norm multiply by (1 + w) */
   int32_t glu_act;       /* activation of the feed-forward's gate: 0 silu, 1 tanh-GELU */
   int32_t side_dim;      /* per-layer token input: width of each layer's slice of the side embedding; 0 = none */
+  int32_t norm_input;    /* 1: pre-norm layers  x <- x + sublayer(norm(x))  (residual_mult, norm_one_plus, side_dim unused) */
+  int32_t norm_scalar;   /* 1: every layer norm and the final norm has ONE weight for all coordinates */
+  int32_t token_shift;   /* 1: the mixer reads h + (h_prev - h) * shift, h_prev = the previous token's normed input
+                               (zeros ahead of position 0; kept per sequence slot and layer run); tensor l<i>.shift */
+  float embed_scale;     /* multiplier of the embedding rows; 0 = 1 */
+  /* layers [loop_start, loop_stop) run loop_times times in a row with the same weights, every pass with its own
+   * caches and states; ahead of pass t the row t of the tensor "loop.step" [loop_times, width] is added to x.
+   * loop_times 0 = no loop.  A "layer run" is one execution of a layer; runs are numbered in execution order. */
+  int32_t loop_start, loop_stop, loop_times;
 } L3StackConfig;
 
 int l3_create_stack(const L3StackConfig* cfg, const L3LayerSpec* layers, L3Model** out);
@@ -174,11 +201,14 @@ int l3_create_stack(const L3StackConfig* cfg, const L3LayerSpec* layers, L3Model
 int l3_load_tensor(L3Model* m, const char* name, const float* host, const int64_t* shape, int ndim);
 /* l3_forward with the logits of chosen rows: rows[i] = b * L + t of the [B, L] block, logits_out
  * [n_rows, vocab] float32.  resid_out (may be NULL, stack handles only): the residual stream after every
- * layer, [n_layers, B * L, width] float32.  Works for Llama handles too (resid_out must be NULL). */
+ * layer run, [n_runs, B * L, width] float32 (l3_stack_runs; = n_layers without a loop). */
 int l3_forward_rows(L3Model* m, const int32_t* ids, int B, int L, int start_pos, const int32_t* rows, int n_rows,
                     float* logits_out, float* resid_out);
-/* Recurrent state of one layer and slot (tests): S [heads, dim, vdim] float32; conv_out (may be NULL)
- * [channels, taps - 1] float32, the convolution's tail, oldest input first. */
+/* Number of layer runs of a stack handle (a layer inside the loop counts once per pass). */
+int l3_stack_runs(L3Model* m, int* n_runs_out);
+/* Recurrent state of one layer run and slot (tests): S [heads, dim, vdim] float32; conv_out (may be NULL)
+ * [channels, taps - 1] float32, the convolution's tail, oldest input first.  L3_MIX_LATENT: S receives the
+ * slot's latent cache [max_seq_len, kv_rank + rot_dim].  `layer` counts layer runs. */
 int l3_read_state(L3Model* m, int layer, int slot, float* S_out, float* conv_out);
 
 /* -- state inspection (tests): the layer's caches in the reference's layout

@@ -19,6 +19,9 @@ def __getattr__(name):  # lazy: importing the package must not require the built
     if name == "Risalix":
         from .risalix import Risalix
         return Risalix
+    if name == "Rakelorn":
+        from .rakelorn import Rakelorn
+        return Rakelorn
     if name in ("StackDecoder", "StackConfig", "LayerSpec"):
         from . import stack as _s
         return getattr(_s, name)

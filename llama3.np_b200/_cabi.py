@@ -24,21 +24,27 @@ class L3Config(C.Structure):
                 ("tp_world", C.c_int32), ("flags", C.c_int32)]
 
 
-MIX_SOFTMAX, MIX_DECAY_LINEAR, MIX_GATED_DELTA = 0, 1, 2
+MIX_SOFTMAX, MIX_DECAY_LINEAR, MIX_GATED_DELTA, MIX_LATENT, MIX_MINGRU = 0, 1, 2, 3, 4
 GLU_SILU, GLU_GELU_TANH = 0, 1
 
 
 class L3LayerSpec(C.Structure):
     _fields_ = [("mixer", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32),
                 ("vdim", C.c_int32), ("conv_taps", C.c_int32), ("rank_decay", C.c_int32), ("rank_gate", C.c_int32),
-                ("ff", C.c_int32), ("scale", C.c_float), ("decay", C.POINTER(C.c_float))]
+                ("ff", C.c_int32), ("scale", C.c_float), ("decay", C.POINTER(C.c_float)),
+                ("q_rank", C.c_int32), ("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("rot_dims", C.c_int32),
+                ("rot_base", C.c_double),
+                ("experts", C.c_int32), ("top", C.c_int32), ("identity", C.c_int32), ("groups", C.c_int32),
+                ("groups_keep", C.c_int32), ("router_scale", C.c_float)]
 
 
 class L3StackConfig(C.Structure):
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("max_seq_len", C.c_int32),
                 ("max_batch_size", C.c_int32), ("dtype", C.c_int32), ("device", C.c_int32), ("flags", C.c_int32),
                 ("norm_eps", C.c_float), ("residual_mult", C.c_float), ("norm_one_plus", C.c_int32),
-                ("glu_act", C.c_int32), ("side_dim", C.c_int32)]
+                ("glu_act", C.c_int32), ("side_dim", C.c_int32),
+                ("norm_input", C.c_int32), ("norm_scalar", C.c_int32), ("token_shift", C.c_int32),
+                ("embed_scale", C.c_float), ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32)]
 
 
 _P = C.c_void_p
@@ -59,6 +65,7 @@ SIGNATURES = {
     "l3_load_tensor": (_I, [_P, C.c_char_p, _F32P, _I64P, _I]),
     "l3_forward_rows": (_I, [_P, _I32P, _I, _I, _I, _I32P, _I, _F32P, _F32P]),
     "l3_read_state": (_I, [_P, _I, _I, _F32P, _F32P]),
+    "l3_stack_runs": (_I, [_P, C.POINTER(_I)]),
     "l3_fill_random": (_I, [_P, C.c_uint64]),
     "l3_save_packed": (_I, [_P, C.c_char_p, C.c_char_p]),
     "l3_load_packed": (_I, [_P, C.c_char_p, C.c_char_p]),

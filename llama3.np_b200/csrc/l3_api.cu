@@ -463,10 +463,11 @@ extern "C" int l3_reset_cache(L3Model* m) {
 
 extern "C" int l3_read_cache(L3Model* m, int layer, float* k_out, float* v_out) {
   if (!m || !m->finalized) return L3_ESTATE;
-  REQUIRE(m, layer >= 0 && layer < m->cfg.n_layers, "layer out of range");
+  REQUIRE(m, layer >= 0 && layer < (m->ll ? (int)m->ll->runs.size() : m->cfg.n_layers), "layer out of range");
   CK(m, cudaSetDevice(m->cfg.device));
-  if (m->ll) {  // a softmax layer of a layer-list handle: its own head count and size
-    const LLLayer& Ly = m->ll->layers[layer];
+  if (m->ll) {  // a softmax layer run of a layer-list handle: its own head count and size
+    const LLLayer& Ly = m->ll->layers[m->ll->runs[layer].layer];
+    const LLState& St = m->ll->state[layer];
     REQUIRE(m, Ly.spec.mixer == L3_MIX_SOFTMAX, "layer %d keeps a recurrent state, not a KV cache (l3_read_state)", layer);
     const int G = Ly.spec.kv_heads, HD = Ly.spec.dim;
     const size_t n = (size_t)m->maxB * G * m->M * HD;
@@ -475,7 +476,7 @@ extern "C" int l3_read_cache(L3Model* m, int layer, float* k_out, float* v_out) 
     for (int which = 0; which < 2; ++which) {
       float* dst = which ? v_out : k_out;
       if (!dst) continue;
-      CK(m, launch_cache_to_ref_layout(which ? Ly.cv : Ly.ck, m->bf16, m->maxB, G, m->M, HD, tmp, m->stream));
+      CK(m, launch_cache_to_ref_layout(which ? St.cv : St.ck, m->bf16, m->maxB, G, m->M, HD, tmp, m->stream));
       CK(m, cudaMemcpyAsync(dst, tmp, n * 4, cudaMemcpyDeviceToHost, m->stream));
       CK(m, cudaStreamSynchronize(m->stream));
     }
@@ -813,7 +814,7 @@ extern "C" int l3_forward_rows(L3Model* m, const int32_t* ids, int B, int L, int
     CK(m, cudaMalloc((void**)&d_rows, (size_t)n_rows * 4));
     CK(m, cudaMemcpyAsync(d_rows, rows, (size_t)n_rows * 4, cudaMemcpyHostToDevice, m->stream));
   }
-  const size_t nres = (size_t)m->cfg.n_layers * B * L * m->D;
+  const size_t nres = m->ll->runs.size() * (size_t)B * L * m->D;
   if (resid_out) CK(m, cudaMalloc((void**)&d_resid, nres * 4));
   CK(m, cudaMemcpyAsync(m->d_fwd_ids, ids, (size_t)B * L * 4, cudaMemcpyHostToDevice, m->stream));
   rc = enqueue_prefill(m, m->d_fwd_ids, B, L, start_pos, n_rows > 0, false, OutSpec{m->d_fwd_arg, 1, m->d_scal + 3, m->d_fwd_next},

@@ -33,9 +33,23 @@ static int pad8(int v) { return (v + 7) & ~7; }
 
 // ------------------------------------------------------------------------------ create
 static int check_spec(const L3StackConfig* c, const L3LayerSpec& s, int i) {
-  REQUIRE(nullptr, s.mixer >= L3_MIX_SOFTMAX && s.mixer <= L3_MIX_GATED_DELTA, "layer %d: unknown mixer %d", i, s.mixer);
+  REQUIRE(nullptr, s.mixer >= L3_MIX_SOFTMAX && s.mixer <= L3_MIX_MINGRU, "layer %d: unknown mixer %d", i, s.mixer);
   REQUIRE(nullptr, s.heads >= 1 && s.dim >= 1 && s.vdim >= 1 && s.ff >= 0, "layer %d: bad sizes", i);
-  if (s.mixer == L3_MIX_SOFTMAX) {
+  REQUIRE(nullptr, s.mixer <= L3_MIX_GATED_DELTA || c->norm_input, "layer %d: this mixer is built for pre-norm layers (norm_input)", i);
+  if (s.experts > 0) {
+    const int n = s.experts + s.identity;
+    REQUIRE(nullptr, c->norm_input, "layer %d: the mixture of experts is built for pre-norm layers (norm_input)", i);
+    REQUIRE(nullptr, s.ff >= 1 && s.identity >= 0 && s.top >= 1 && s.top <= n && n <= 1024, "layer %d: bad expert counts", i);
+    REQUIRE(nullptr, s.groups >= 1 && n % s.groups == 0 && s.groups_keep >= 1 && s.groups_keep <= s.groups, "layer %d: bad expert groups", i);
+  }
+  if (s.mixer == L3_MIX_LATENT) {
+    REQUIRE(nullptr, s.q_rank >= 1 && s.kv_rank >= 1 && s.rot_dim >= 0 && s.rot_dims >= 0 && s.rot_dims <= s.rot_dim && s.rot_dims % 2 == 0,
+            "layer %d: bad latent / rotary sizes", i);
+    REQUIRE(nullptr, s.rot_dims == 0 || s.rot_base > 0, "layer %d: rotary base must be positive", i);
+    REQUIRE(nullptr, latent_attn_supported(s.kv_rank + s.rot_dim, s.kv_rank), "layer %d: latent row of %d + %d entries unsupported", i, s.kv_rank, s.rot_dim);
+  } else if (s.mixer == L3_MIX_MINGRU) {
+    REQUIRE(nullptr, s.heads == 1 && s.vdim == 1, "layer %d: the element-wise recurrence has heads = vdim = 1", i);
+  } else if (s.mixer == L3_MIX_SOFTMAX) {
     REQUIRE(nullptr, s.kv_heads >= 1 && s.heads % s.kv_heads == 0, "layer %d: heads %% kv_heads != 0", i);
     REQUIRE(nullptr, s.vdim == s.dim, "layer %d: the values of this attention are its keys, so vdim must equal dim", i);
   } else if (s.mixer == L3_MIX_DECAY_LINEAR) {
@@ -60,6 +74,10 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
     const int rc = check_spec(c, specs[i], i);
     if (rc != L3_OK) return rc;
   }
+  REQUIRE(nullptr, c->loop_times >= 0 && (c->loop_times == 0 || (c->loop_start >= 0 && c->loop_start <= c->loop_stop && c->loop_stop <= c->n_layers)),
+          "bad loop bounds");
+  REQUIRE(nullptr, !c->norm_input || c->side_dim == 0, "pre-norm stacks have no per-layer token input");
+  REQUIRE(nullptr, c->norm_input || (!c->token_shift && !c->norm_scalar), "token shift and single-weight norms are built for pre-norm stacks");
   L3Model* m = new L3Model();
   LayerList* ll = m->ll = new LayerList();
   ll->cfg = *c;
@@ -98,7 +116,25 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
     const L3LayerSpec& s = L.spec;
     const int H = s.heads, G = s.mixer == L3_MIX_DECAY_LINEAR ? s.heads : s.kv_heads, DK = s.dim, DV = s.vdim;
     L.spec.kv_heads = G;
-    if (s.mixer == L3_MIX_SOFTMAX) {
+    if (s.mixer == L3_MIX_LATENT) {
+      // dq | dkv | g rows, every segment on a multiple of 8 columns of the projection's output
+      const int Dk = s.kv_rank + s.rot_dim;
+      L.off_q = 0; L.off_k = pad8(s.q_rank); L.off_g = pad8(L.off_k + Dk); L.n_in = pad8(L.off_g + H);
+      AL(L.q_norm, (size_t)s.q_rank * 4);
+      AL(L.k_norm, (size_t)s.kv_rank * 4);
+      AL(L.w_uq, (size_t)H * (DK + s.rot_dim) * s.q_rank * w);
+      AL(L.w_uk, (size_t)H * DK * s.kv_rank * w);
+      AL(L.w_uv, (size_t)H * DV * s.kv_rank * w);
+      AL(L.inv_freq, (size_t)std::max(1, s.rot_dims / 2) * 4);
+      std::vector<float> f(std::max(1, s.rot_dims / 2), 0.f);
+      for (int j = 0; j < s.rot_dims / 2; ++j) f[j] = (float)pow(s.rot_base, -2.0 * j / s.rot_dims);
+      if ((e = cudaMemcpy(L.inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess) {
+        set_err(nullptr, "rotary table upload: %s", cudaGetErrorString(e)); l3_destroy(m); return L3_ECUDA;
+      }
+    } else if (s.mixer == L3_MIX_MINGRU) {
+      L.off_b = 0; L.off_v = pad8(DK); L.off_g = pad8(L.off_v + DK); L.n_in = pad8(L.off_g + DK);  // z | x | g
+      AL(L.in_bias, (size_t)2 * DK * 4);
+    } else if (s.mixer == L3_MIX_SOFTMAX) {
       L.off_q = 0; L.off_k = H * DK; L.off_g = L.off_k + G * DK; L.n_in = L.off_g + H;
       AL(L.q_norm, (size_t)H * DK * 4);
       AL(L.k_norm, (size_t)G * DK * 4);
@@ -124,9 +160,17 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
     }
     AL(L.w_in, (size_t)L.n_in * W * w);
     cudaMemset(L.w_in, 0, (size_t)L.n_in * W * w);  // padding rows project to zero
-    AL(L.w_o, (size_t)W * H * DV * w);
+    const int n_ctx = s.mixer == L3_MIX_MINGRU ? DK : H * DV;  // columns the output projection reads
+    AL(L.w_o, (size_t)W * n_ctx * w);
     AL(L.norm1, (size_t)W * 4);
-    if (s.ff > 0) {
+    if (c->token_shift) AL(L.shift, (size_t)W * 4);
+    if (s.experts > 0) {
+      AL(L.w13, (size_t)s.experts * s.ff * W * w);
+      AL(L.w2, (size_t)W * s.experts * s.ff * w);
+      AL(L.norm2, (size_t)W * 4);
+      AL(L.router, (size_t)(s.experts + s.identity) * W * 4);
+      AL(L.correction, (size_t)(s.experts + s.identity) * 4);
+    } else if (s.ff > 0) {
       AL(L.w13, (size_t)2 * s.ff * W * w);
       AL(L.w2, (size_t)W * s.ff * w);
       AL(L.norm2, (size_t)W * 4);
@@ -138,9 +182,22 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
     }
     ll->max_in = std::max(ll->max_in, L.n_in);
     ll->max_o = std::max(ll->max_o, std::max(H * DV, H * DK));
-    ll->max_ff = std::max(ll->max_ff, s.ff);
+    if (s.mixer == L3_MIX_LATENT) ll->max_o = std::max(ll->max_o, H * s.kv_rank);
+    ll->max_ff = std::max(ll->max_ff, s.experts > 0 ? s.experts * s.ff : s.ff);
   }
+  if (c->loop_times > 0) AL(ll->loop_step, (size_t)c->loop_times * W * 4);
 #undef AL
+  // execution order: the layers ahead of the loop, the looped block loop_times times, the rest
+  auto run = [&](int layer, int pass) { LLRun r; r.layer = layer; r.pass = pass; ll->runs.push_back(r); };
+  if (c->loop_times > 0) {
+    for (int i = 0; i < c->loop_start; ++i) run(i, -1);
+    for (int t = 0; t < c->loop_times; ++t)
+      for (int i = c->loop_start; i < c->loop_stop; ++i) run(i, i == c->loop_start ? t : -1);
+    for (int i = c->loop_stop; i < c->n_layers; ++i) run(i, -1);
+  } else {
+    for (int i = 0; i < c->n_layers; ++i) run(i, -1);
+  }
+  ll->state.resize(ll->runs.size());
   ll->slot_pos.assign(c->max_batch_size, 0);
   *out = m;
   return L3_OK;
@@ -154,6 +211,7 @@ struct LLPlace {
   int64_t rows = 0, cols = 1;
   int row0 = 0, row_stride = 1, ld = 1;
   bool one_plus = false; // stored as 1 + w
+  bool broadcast = false;  // the checkpoint holds one number, the device vector `rows` copies of it
   float scale = 0.f, bias = 0.f;  // random init
 };
 
@@ -171,9 +229,22 @@ static bool ll_place(L3Model* m, const std::string& name, LLPlace* p) {
     p->dst = d; p->wt = false; p->rows = n; p->cols = 1; p->ld = 1; p->bias = bias; p->scale = scale; p->one_plus = one_plus;
     return d != nullptr;
   };
-  if (name == "embed") { const bool ok = mat(m->embed, V, W); p->scale = 1.0f; return ok; }
+  const bool pre = ll->cfg.norm_input != 0;
+  // a layer norm's weight: [width], or one number spread over the vector
+  auto norm = [&](float* d) {
+    const bool ok = vec(d, W, op && !pre ? 0.f : 1.f, 0.1f, op && !pre);
+    p->broadcast = ll->cfg.norm_scalar != 0;
+    return ok;
+  };
+  // fp32 matrix (router tables, step vectors)
+  auto fmat = [&](float* d, int64_t r, int64_t c, float scale) {
+    p->dst = d; p->wt = false; p->rows = r; p->cols = c; p->ld = (int)c; p->scale = scale;
+    return d != nullptr;
+  };
+  if (name == "embed") { const bool ok = mat(m->embed, V, W); p->scale = pre ? 0.1f : 1.0f; return ok; }
   if (name == "head") return mat(m->lm_head, V, W);
-  if (name == "final.norm") return vec(m->norm_final, W, op ? 0.f : 1.f, 0.1f, op);
+  if (name == "final.norm") return norm(m->norm_final);
+  if (name == "loop.step") return ll->loop_step && fmat(ll->loop_step, ll->cfg.loop_times, W, 0.3f);
   if (name == "side.embed") { const bool ok = sd && mat(ll->side_embed, V, (int64_t)NL * sd); p->scale = 1.0f; return ok; }
   int li = -1, n = 0;
   if (sscanf(name.c_str(), "l%d.%n", &li, &n) < 1 || n == 0 || li < 0 || li >= NL) return false;
@@ -181,16 +252,53 @@ static bool ll_place(L3Model* m, const std::string& name, LLPlace* p) {
   LLLayer& L = ll->layers[li];
   const L3LayerSpec& s = L.spec;
   const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
-  if (r == "norm1") return vec(L.norm1, W, op ? 0.f : 1.f, 0.1f, op);
-  if (r == "norm2") return s.ff > 0 && vec(L.norm2, W, op ? 0.f : 1.f, 0.1f, op);
-  if (r == "mlp.gate") return s.ff > 0 && mat(L.w13, s.ff, W, 0, 2);
-  if (r == "mlp.up") return s.ff > 0 && mat(L.w13, s.ff, W, 1, 2);
-  if (r == "mlp.down") return s.ff > 0 && mat(L.w2, W, s.ff);
+  if (r == "norm1") return norm(L.norm1);
+  if (r == "norm2") return s.ff > 0 && norm(L.norm2);
+  if (r == "shift") return L.shift && vec(L.shift, W, 0.5f, 0.5f);
+  if (s.experts > 0) {
+    const int n = s.experts + s.identity;
+    if (r == "mlp.router") return fmat(L.router, n, W, 3.0f / sqrtf((float)W));
+    if (r == "mlp.correction") return vec(L.correction, n, 0.f, 0.05f);
+    int e = -1, n2 = 0;
+    if (sscanf(r.c_str(), "mlp.e%d.%n", &e, &n2) >= 1 && n2 > 0 && e >= 0 && e < s.experts) {
+      const std::string part = r.substr(n2);
+      if (part == "up") return mat(L.w13, s.ff, W, e * s.ff, 1);
+      if (part == "down") {  // columns [e ff, (e + 1) ff) of the [width, experts * ff] matrix
+        const bool ok = mat((char*)L.w2 + (size_t)e * s.ff * wb(m), W, s.ff);
+        p->ld = s.experts * s.ff;
+        return ok;
+      }
+    }
+    if (r.compare(0, 4, "mlp.") == 0) return false;
+  } else {
+    if (r == "mlp.gate") return s.ff > 0 && mat(L.w13, s.ff, W, 0, 2);
+    if (r == "mlp.up") return s.ff > 0 && mat(L.w13, s.ff, W, 1, 2);
+    if (r == "mlp.down") return s.ff > 0 && mat(L.w2, W, s.ff);
+  }
   if (r == "side.gate") return sd && mat(L.side_gate, sd, W);
   if (r == "side.proj") return sd && mat(L.side_proj, W, sd);
   if (r == "side.norm") return sd && vec(L.side_norm, W, 1.f, 0.1f);
-  if (r == "mix.o") return mat(L.w_o, W, (int64_t)H * DV);
+  if (r == "mix.o") return mat(L.w_o, W, s.mixer == L3_MIX_MINGRU ? (int64_t)DK : (int64_t)H * DV);
   auto seg = [&](int off, int64_t rows) { const bool ok = mat(L.w_in, rows, W, off, 1); return ok; };
+  if (s.mixer == L3_MIX_LATENT) {
+    if (r == "mix.dq") return seg(L.off_q, s.q_rank);
+    if (r == "mix.dkv") { const bool ok = seg(L.off_k, (int64_t)s.kv_rank + s.rot_dim); p->scale *= 2.f; return ok; }
+    if (r == "mix.g") return seg(L.off_g, H);
+    if (r == "mix.dq.norm") return vec(L.q_norm, s.q_rank, 1.f, 0.1f);
+    if (r == "mix.dkv.norm") return vec(L.k_norm, s.kv_rank, 1.f, 0.1f);
+    if (r == "mix.uq") { const bool ok = mat(L.w_uq, (int64_t)H * (DK + s.rot_dim), s.q_rank); p->scale *= 2.f; return ok; }
+    if (r == "mix.uk") { const bool ok = mat(L.w_uk, (int64_t)H * DK, s.kv_rank); p->scale *= 2.f; return ok; }
+    if (r == "mix.uv") return mat(L.w_uv, (int64_t)H * DV, s.kv_rank);
+    return false;
+  }
+  if (s.mixer == L3_MIX_MINGRU) {
+    if (r == "mix.z") return seg(L.off_b, DK);
+    if (r == "mix.x") return seg(L.off_v, DK);
+    if (r == "mix.g") return seg(L.off_g, DK);
+    if (r == "mix.z.b") return vec(L.in_bias, DK, 0.f, 1.0f);
+    if (r == "mix.x.b") return vec(L.in_bias + DK, DK, 0.f, 0.5f);
+    return false;
+  }
   if (s.mixer == L3_MIX_SOFTMAX) {
     if (r == "mix.q") return seg(L.off_q, (int64_t)H * DK);
     if (r == "mix.k") return seg(L.off_k, (int64_t)G * DK);
@@ -234,15 +342,25 @@ static std::vector<std::string> ll_expected(const L3Model* m) {
   const LayerList* ll = m->ll;
   std::vector<std::string> v = {"embed", "head", "final.norm"};
   if (ll->cfg.side_dim) v.push_back("side.embed");
+  if (ll->loop_step) v.push_back("loop.step");
   for (int i = 0; i < ll->cfg.n_layers; ++i) {
     const L3LayerSpec& s = ll->layers[i].spec;
     const std::string p = "l" + std::to_string(i) + ".";
     std::vector<const char*> names = {"norm1", "mix.o"};
-    if (s.mixer == L3_MIX_SOFTMAX) names.insert(names.end(), {"mix.q", "mix.k", "mix.g", "mix.q.norm", "mix.k.norm"});
+    if (ll->cfg.token_shift) names.push_back("shift");
+    if (s.mixer == L3_MIX_LATENT) names.insert(names.end(), {"mix.dq", "mix.dq.norm", "mix.uq", "mix.dkv", "mix.dkv.norm", "mix.uk", "mix.uv", "mix.g"});
+    else if (s.mixer == L3_MIX_MINGRU) names.insert(names.end(), {"mix.z", "mix.z.b", "mix.x", "mix.x.b", "mix.g"});
+    else if (s.mixer == L3_MIX_SOFTMAX) names.insert(names.end(), {"mix.q", "mix.k", "mix.g", "mix.q.norm", "mix.k.norm"});
     else if (s.mixer == L3_MIX_DECAY_LINEAR) names.insert(names.end(), {"mix.q", "mix.k", "mix.v", "mix.g", "mix.norm"});
     else names.insert(names.end(), {"mix.q", "mix.k", "mix.v", "mix.b", "mix.a1", "mix.a2", "mix.g1", "mix.g2", "mix.norm",
                                     "mix.A_log", "mix.dt_bias", "mix.q.conv", "mix.k.conv", "mix.v.conv"});
-    if (s.ff > 0) names.insert(names.end(), {"norm2", "mlp.gate", "mlp.up", "mlp.down"});
+    if (s.experts > 0) {
+      names.insert(names.end(), {"norm2", "mlp.router", "mlp.correction"});
+      for (int e = 0; e < s.experts; ++e) {
+        v.push_back(p + "mlp.e" + std::to_string(e) + ".up");
+        v.push_back(p + "mlp.e" + std::to_string(e) + ".down");
+      }
+    } else if (s.ff > 0) names.insert(names.end(), {"norm2", "mlp.gate", "mlp.up", "mlp.down"});
     if (ll->cfg.side_dim) names.insert(names.end(), {"side.gate", "side.proj", "side.norm"});
     for (auto nme : names) v.push_back(p + nme);
   }
@@ -258,6 +376,13 @@ extern "C" int l3_load_tensor(L3Model* m, const char* name, const float* host, c
   REQUIRE(m, ll_place(m, name, &p), "tensor '%s' does not belong to this model", name);
   REQUIRE(m, ndim == 1 || ndim == 2, "'%s': expected a vector or a matrix, got %d dimensions", name, ndim);
   const int64_t rows = shape[0], cols = ndim > 1 ? shape[1] : 1;
+  if (p.broadcast) {
+    REQUIRE(m, rows * cols == 1, "'%s': expected a single number, got [%lld, %lld]", name, (long long)rows, (long long)cols);
+    const std::vector<float> v((size_t)p.rows, host[0]);
+    CK(m, cudaMemcpy(p.dst, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
+    m->ll->loaded.insert(name);
+    return L3_OK;
+  }
   REQUIRE(m, rows == p.rows && cols == p.cols, "shape mismatch for '%s': got [%lld, %lld], want [%lld, %lld]", name,
           (long long)rows, (long long)cols, (long long)p.rows, (long long)p.cols);
   const size_t STAGE = (size_t)256 << 20;
@@ -300,24 +425,41 @@ int ll_finalize(L3Model* m) {
     if (!ll->loaded.count(name)) { set_err(m, "tensor '%s' was never loaded", name.c_str()); return L3_ESTATE; }
   if (m->stage) { cudaFree(m->stage); m->stage = nullptr; }
   const size_t kvb = m->bf16 ? 2 : 4;
-  int max_rq = 1, max_rk = 1, max_rv = 1, max_rg = 1, max_h = 1, max_aux = 1;
+  int max_rq = 1, max_rk = 1, max_rv = 1, max_rg = 1, max_h = 1, max_aux = 1, max_qlat = 0, max_top = 0, max_exp = 0, max_hid = 1;
+  for (size_t ri = 0; ri < ll->runs.size(); ++ri) {
+    const LLLayer& L = ll->layers[ll->runs[ri].layer];
+    LLState& St = ll->state[ri];
+    const L3LayerSpec& s = L.spec;
+    const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
+    if (ll->cfg.token_shift) CK(m, cudaMalloc((void**)&St.hprev, (size_t)m->maxB * m->D * 4));
+    if (s.mixer == L3_MIX_LATENT) {
+      CK(m, cudaMalloc(&St.lat, (size_t)m->maxB * m->M * (s.kv_rank + s.rot_dim) * kvb));
+    } else if (s.mixer == L3_MIX_SOFTMAX) {
+      const size_t bytes = (size_t)m->maxB * G * m->M * DK * kvb;
+      CK(m, cudaMalloc(&St.ck, bytes));
+      CK(m, cudaMalloc(&St.cv, bytes));
+    } else {
+      CK(m, cudaMalloc((void**)&St.S, (size_t)m->maxB * H * DK * DV * 4));
+      if (s.mixer == L3_MIX_GATED_DELTA) {
+        const int C = 2 * G * DK + H * DV;
+        CK(m, cudaMalloc((void**)&St.conv_tail, std::max<size_t>(16, (size_t)m->maxB * C * (s.conv_taps - 1) * 4)));
+      }
+    }
+  }
   for (auto& L : ll->layers) {
     const L3LayerSpec& s = L.spec;
     const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
     if (s.mixer == L3_MIX_SOFTMAX) {
-      const size_t bytes = (size_t)m->maxB * G * m->M * DK * kvb;
-      CK(m, cudaMalloc(&L.ck, bytes));
-      CK(m, cudaMalloc(&L.cv, bytes));
       max_rq = std::max(max_rq, H * DK);
-    } else {
-      CK(m, cudaMalloc((void**)&L.S, (size_t)m->maxB * H * DK * DV * 4));
-      if (s.mixer == L3_MIX_GATED_DELTA) {
-        const int C = 2 * G * DK + H * DV;
-        CK(m, cudaMalloc((void**)&L.conv_tail, std::max<size_t>(16, (size_t)m->maxB * C * (s.conv_taps - 1) * 4)));
-        max_rq = std::max(max_rq, G * DK); max_rk = std::max(max_rk, G * DK); max_rv = std::max(max_rv, H * DV);
-        max_rg = std::max(max_rg, H * DK); max_h = std::max(max_h, H); max_aux = std::max(max_aux, H * DK + H * DV);
-      }
+    } else if (s.mixer == L3_MIX_GATED_DELTA) {
+      max_rq = std::max(max_rq, G * DK); max_rk = std::max(max_rk, G * DK); max_rv = std::max(max_rv, H * DV);
+      max_rg = std::max(max_rg, H * DK); max_h = std::max(max_h, H); max_aux = std::max(max_aux, H * DK + H * DV);
+    } else if (s.mixer == L3_MIX_LATENT) {
+      max_rq = std::max(max_rq, H * (DK + s.rot_dim));
+      max_aux = std::max(max_aux, s.q_rank);
+      max_qlat = std::max(max_qlat, H * (s.kv_rank + s.rot_dim));
     }
+    if (s.experts > 0) { max_top = std::max(max_top, s.top); max_exp = std::max(max_exp, s.experts); max_hid = std::max(max_hid, s.top * s.ff); }
   }
   const int W = m->D, sd = ll->cfg.side_dim;
   const int64_t want = (int64_t)m->maxB * m->M;
@@ -328,7 +470,7 @@ int ll_finalize(L3Model* m) {
   CK(m, cudaMalloc((void**)&m->xn, ct * W * 4));  // sublayer output before its norm
   CK(m, cudaMalloc((void**)&m->q, ct * max_rq * 4));
   CK(m, cudaMalloc((void**)&m->ctx, ct * ll->max_o * 4));
-  CK(m, cudaMalloc((void**)&m->h, ct * std::max(1, ll->max_ff) * 4));
+  CK(m, cudaMalloc((void**)&m->h, std::max(ct * std::max(1, ll->max_ff), (size_t)8 * max_hid) * 4));
   CK(m, cudaMalloc((void**)&m->xlast, (size_t)m->maxB * W * 4));
   CK(m, cudaMalloc((void**)&m->logits, (size_t)m->maxB * m->VS * 4));
   CK(m, cudaMalloc((void**)&ll->pin, ct * ll->max_in * 4));
@@ -339,6 +481,13 @@ int ll_finalize(L3Model* m) {
   CK(m, cudaMalloc((void**)&ll->rbeta, ct * max_h * 4));
   CK(m, cudaMalloc((void**)&ll->o, ct * ll->max_o * 4));
   CK(m, cudaMalloc((void**)&ll->sg, ct * std::max(1, sd) * 4));
+  if (max_qlat) CK(m, cudaMalloc((void**)&ll->qlat, ct * max_qlat * 4));
+  if (max_top) {
+    CK(m, cudaMalloc((void**)&ll->moe_sel, ct * max_top * 4));
+    CK(m, cudaMalloc((void**)&ll->moe_w, ct * max_top * 4));
+    CK(m, cudaMalloc((void**)&ll->moe_dense, ct * max_exp * 4));
+    CK(m, cudaMalloc((void**)&ll->moe_idw, ct * 4));
+  }
   for (const LLLayer& L : ll->layers)
     if (L.spec.mixer == L3_MIX_DECAY_LINEAR && recur_chunk_shape(L.spec.dim, L.spec.vdim) && ct >= 128)
       ll->chunk_ws_floats = std::max(ll->chunk_ws_floats, (ct / 64 + m->maxB) * (size_t)L.spec.heads * L.spec.dim * L.spec.vdim);
@@ -357,11 +506,13 @@ int ll_finalize(L3Model* m) {
     CK(m, cudaMalloc(&m->h16, ct * std::max(1, ll->max_ff) * 2));
     CK(m, cudaMalloc(&m->xlast16, (size_t)m->maxB * W * 2));
     CK(m, cudaMalloc(&ll->sg16, ct * std::max(1, sd) * 2));
+    if (max_qlat) CK(m, cudaMalloc(&ll->aux16, ct * max_aux * 2));
   }
   m->max_split = 32;
   int max_hn = 1, max_hd = 1;
   for (auto& L : ll->layers)
     if (L.spec.mixer == L3_MIX_SOFTMAX) { max_hn = std::max(max_hn, L.spec.heads); max_hd = std::max(max_hd, L.spec.dim); }
+    else if (L.spec.mixer == L3_MIX_LATENT) { max_hn = std::max(max_hn, L.spec.heads); max_hd = std::max(max_hd, L.spec.kv_rank); }
   CK(m, cudaMalloc((void**)&m->part_o, (size_t)m->maxB * max_hn * m->max_split * max_hd * 4));
   CK(m, cudaMalloc((void**)&m->part_ml, (size_t)m->maxB * max_hn * m->max_split * 2 * 4));
   CK(m, cudaMalloc((void**)&m->attn_cnt, (size_t)m->maxB * max_hn * 4));
@@ -396,8 +547,11 @@ void ll_destroy(L3Model* m) {
   for (auto& L : ll->layers) {
     fr(L.w_in); fr(L.w_o); fr(L.w_a2); fr(L.w_g2); fr(L.w13); fr(L.w2); fr(L.side_gate); fr(L.side_proj);
     fr(L.norm1); fr(L.norm2); fr(L.side_norm); fr(L.mix_norm); fr(L.q_norm); fr(L.k_norm); fr(L.conv_w);
-    fr(L.A_log); fr(L.dt_bias); fr(L.decay); fr(L.ck); fr(L.cv); fr(L.S); fr(L.conv_tail);
+    fr(L.A_log); fr(L.dt_bias); fr(L.decay);
+    fr(L.w_uq); fr(L.w_uk); fr(L.w_uv); fr(L.inv_freq); fr(L.in_bias); fr(L.shift); fr(L.router); fr(L.correction);
   }
+  for (auto& St : ll->state) { fr(St.ck); fr(St.cv); fr(St.S); fr(St.conv_tail); fr(St.lat); fr(St.hprev); }
+  fr(ll->loop_step); fr(ll->qlat); fr(ll->aux16); fr(ll->moe_sel); fr(ll->moe_w); fr(ll->moe_dense); fr(ll->moe_idw);
   fr(ll->pin); fr(ll->aux); fr(ll->rk); fr(ll->rv); fr(ll->rg); fr(ll->rbeta); fr(ll->o); fr(ll->sg); fr(ll->sg16); fr(ll->x2); fr(ll->chunk_ws);
   delete ll;
   m->ll = nullptr;
@@ -406,19 +560,25 @@ void ll_destroy(L3Model* m) {
 int ll_reset_slots(L3Model* m, int slot0, int n, bool kv_too) {
   LayerList* ll = m->ll;
   const size_t kvb = m->bf16 ? 2 : 4;
-  for (auto& L : ll->layers) {
-    const L3LayerSpec& s = L.spec;
-    if (s.mixer == L3_MIX_SOFTMAX) {
+  for (size_t ri = 0; ri < ll->runs.size(); ++ri) {
+    const L3LayerSpec& s = ll->layers[ll->runs[ri].layer].spec;
+    LLState& St = ll->state[ri];
+    if (St.hprev) CK(m, cudaMemsetAsync(St.hprev + (size_t)slot0 * m->D, 0, (size_t)n * m->D * 4, m->stream));
+    if (s.mixer == L3_MIX_LATENT) {
       if (!kv_too) continue;  // rows past a slot's position are never read: a new sequence overwrites them
+      const size_t per = (size_t)m->M * (s.kv_rank + s.rot_dim) * kvb;
+      CK(m, cudaMemsetAsync((char*)St.lat + slot0 * per, 0, n * per, m->stream));
+    } else if (s.mixer == L3_MIX_SOFTMAX) {
+      if (!kv_too) continue;
       const size_t per = (size_t)s.kv_heads * m->M * s.dim * kvb;
-      CK(m, cudaMemsetAsync((char*)L.ck + slot0 * per, 0, n * per, m->stream));
-      CK(m, cudaMemsetAsync((char*)L.cv + slot0 * per, 0, n * per, m->stream));
+      CK(m, cudaMemsetAsync((char*)St.ck + slot0 * per, 0, n * per, m->stream));
+      CK(m, cudaMemsetAsync((char*)St.cv + slot0 * per, 0, n * per, m->stream));
     } else {
       const size_t per = (size_t)s.heads * s.dim * s.vdim;
-      CK(m, cudaMemsetAsync(L.S + slot0 * per, 0, n * per * 4, m->stream));
+      CK(m, cudaMemsetAsync(St.S + slot0 * per, 0, n * per * 4, m->stream));
       if (s.mixer == L3_MIX_GATED_DELTA && s.conv_taps > 1) {
         const size_t pc = (size_t)(2 * s.kv_heads * s.dim + s.heads * s.vdim) * (s.conv_taps - 1);
-        CK(m, cudaMemsetAsync(L.conv_tail + slot0 * pc, 0, n * pc * 4, m->stream));
+        CK(m, cudaMemsetAsync(St.conv_tail + slot0 * pc, 0, n * pc * 4, m->stream));
       }
     }
   }
@@ -442,21 +602,43 @@ int ll_begin_call(L3Model* m, int B, int L, int start_pos) {
   return L3_OK;
 }
 
+extern "C" int l3_stack_runs(L3Model* m, int* n_runs_out) {
+  if (!m || !n_runs_out) return L3_EINVAL;
+  REQUIRE(m, m->ll != nullptr, "l3_stack_runs needs a handle made by l3_create_stack");
+  *n_runs_out = (int)m->ll->runs.size();
+  return L3_OK;
+}
+
 extern "C" int l3_read_state(L3Model* m, int layer, int slot, float* S_out, float* conv_out) {
   if (!m || !m->finalized) return L3_ESTATE;
   REQUIRE(m, m->ll != nullptr, "l3_read_state needs a handle made by l3_create_stack");
-  REQUIRE(m, layer >= 0 && layer < m->cfg.n_layers && slot >= 0 && slot < m->maxB, "layer / slot out of range");
-  const LLLayer& L = m->ll->layers[layer];
+  REQUIRE(m, layer >= 0 && layer < (int)m->ll->runs.size() && slot >= 0 && slot < m->maxB, "layer run / slot out of range");
+  const LLLayer& L = m->ll->layers[m->ll->runs[layer].layer];
+  const LLState& St = m->ll->state[layer];
   const L3LayerSpec& s = L.spec;
-  REQUIRE(m, s.mixer != L3_MIX_SOFTMAX, "layer %d keeps a KV cache, not a recurrent state (l3_read_cache)", layer);
+  REQUIRE(m, s.mixer != L3_MIX_SOFTMAX, "layer run %d keeps a KV cache, not a recurrent state (l3_read_cache)", layer);
   CK(m, cudaSetDevice(m->cfg.device));
   CK(m, cudaStreamSynchronize(m->stream));
+  if (s.mixer == L3_MIX_LATENT) {
+    REQUIRE(m, !conv_out, "layer run %d has no convolution", layer);
+    const size_t per = (size_t)m->M * (s.kv_rank + s.rot_dim);
+    if (!S_out) return L3_OK;
+    if (!m->bf16) { CK(m, cudaMemcpy(S_out, (const float*)St.lat + slot * per, per * 4, cudaMemcpyDeviceToHost)); return L3_OK; }
+    float* tmp = nullptr;
+    CK(m, cudaMalloc((void**)&tmp, per * 4));
+    cudaError_t e = launch_unpack_bf16((const bf16*)St.lat + slot * per, (int64_t)per, tmp, m->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(S_out, tmp, per * 4, cudaMemcpyDeviceToHost, m->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    cudaFree(tmp);
+    CK(m, e);
+    return L3_OK;
+  }
   const size_t per = (size_t)s.heads * s.dim * s.vdim;
-  if (S_out) CK(m, cudaMemcpy(S_out, L.S + slot * per, per * 4, cudaMemcpyDeviceToHost));
+  if (S_out) CK(m, cudaMemcpy(S_out, St.S + slot * per, per * 4, cudaMemcpyDeviceToHost));
   if (conv_out) {
-    REQUIRE(m, s.mixer == L3_MIX_GATED_DELTA, "layer %d has no convolution", layer);
+    REQUIRE(m, s.mixer == L3_MIX_GATED_DELTA, "layer run %d has no convolution", layer);
     const size_t pc = (size_t)(2 * s.kv_heads * s.dim + s.heads * s.vdim) * (s.conv_taps - 1);
-    if (pc) CK(m, cudaMemcpy(conv_out, L.conv_tail + slot * pc, pc * 4, cudaMemcpyDeviceToHost));
+    if (pc) CK(m, cudaMemcpy(conv_out, St.conv_tail + slot * pc, pc * 4, cudaMemcpyDeviceToHost));
   }
   return L3_OK;
 }
@@ -528,6 +710,110 @@ static EpiArgs store_to(float* out, void* out16, int ld) {
   return e;
 }
 
+// ------------------------------------------------------------------------------ pre-norm layers
+// x <- x + mixer(shift(norm1(x)));  x <- x + ff(norm2(x)).  The residual stream stays in m->x (fp32); the normed rows
+// live in m->xn (+ the bf16 mirror m->xn16 for the tensor-core projections); the sublayers' output projections add
+// into x in their epilogue.
+static EpiArgs resid_into(float* x, int ld) {
+  EpiArgs e{};
+  e.out = x; e.resid = x; e.ld_out = ld;
+  return e;
+}
+
+static int ll_enqueue_prenorm(L3Model* m, int B, int L, float* d_resid) {
+  LayerList* ll = m->ll;
+  const int ntok = B * L, W = m->D;
+  const float eps = ll->cfg.norm_eps;
+  int* d_pos = m->d_scal + 0;
+  float* hn = m->xn;
+  bf16* hn16 = (bf16*)m->xn16;  // null in fp32 mode
+  int rc;
+  ll->xcur = m->x;
+  if (ll->cfg.embed_scale != 0.f && ll->cfg.embed_scale != 1.f) LAUNCH(m, launch_scale_add_rows(m->x, ll->cfg.embed_scale, nullptr, ntok, W, m->stream));
+  for (int ri = 0; ri < (int)ll->runs.size(); ++ri) {
+    LLLayer& Ly = ll->layers[ll->runs[ri].layer];
+    LLState& St = ll->state[ri];
+    const L3LayerSpec& s = Ly.spec;
+    const int H = s.heads, DK = s.dim, DV = s.vdim;
+    if (ll->runs[ri].pass >= 0)
+      LAUNCH(m, launch_scale_add_rows(m->x, 1.0f, ll->loop_step + (size_t)ll->runs[ri].pass * W, ntok, W, m->stream));
+    LAUNCH(m, launch_prenorm_shift(m->x, Ly.norm1, eps, Ly.shift, St.hprev, B, L, W, hn, hn16, m->stream));
+    // every projection of the mixer's input in one GEMM
+    if ((rc = ll_linear(m, Ly.w_in, hn, hn16, 0, ntok, Ly.n_in, W, EPI_STORE, store_to(ll->pin, nullptr, Ly.n_in))) != L3_OK) return rc;
+    int n_ctx = H * DV;
+    if (s.mixer == L3_MIX_LATENT) {
+      const int Dk = s.kv_rank + s.rot_dim, nq = H * (DK + s.rot_dim);
+      LatentPrepArgs pa{};
+      pa.proj = ll->pin; pa.ld = Ly.n_in; pa.k_off = Ly.off_k; pa.wq = Ly.q_norm; pa.wk = Ly.k_norm; pa.eps = eps;
+      pa.cq = ll->aux; pa.cq16 = (bf16*)ll->aux16; pa.cache = St.lat; pa.inv_freq = Ly.inv_freq; pa.pos_ptr = d_pos;
+      pa.L = L; pa.M = m->M; pa.q_rank = s.q_rank; pa.kv_rank = s.kv_rank; pa.rot_dim = s.rot_dim; pa.rot_dims = s.rot_dims;
+      LAUNCH(m, launch_latent_prep(pa, ntok, m->bf16, m->stream));
+      if ((rc = ll_linear(m, Ly.w_uq, ll->aux, ll->aux16, 0, ntok, nq, s.q_rank, EPI_STORE, store_to(m->q, nullptr, nq))) != L3_OK) return rc;
+      // queries onto the latent: qlat[r, h] = [Wuk_h^T q_c | rot(q_r)]
+      HeadGemmArgs ga{};
+      ga.A = m->q; ga.lda = nq; ga.a_hs = DK + s.rot_dim;
+      ga.W = Ly.w_uk; ga.w_hs = (int64_t)DK * s.kv_rank; ga.w_ks = s.kv_rank; ga.w_js = 1;
+      ga.C = ll->qlat; ga.C16 = nullptr; ga.ldc = H * Dk; ga.c_hs = Dk;
+      ga.rows = ntok; ga.H = H; ga.J = s.kv_rank; ga.K = DK;
+      LAUNCH(m, launch_head_gemm(ga, m->bf16, m->stream));
+      if (s.rot_dim > 0)
+        LAUNCH(m, launch_latent_q_rope(m->q, ll->qlat, Ly.inv_freq, d_pos, ntok, L, H, DK, s.rot_dim, s.rot_dims, s.kv_rank, m->stream));
+      LatentAttnArgs at{};
+      at.q = ll->qlat; at.cache = St.lat; at.out = ll->o; at.gate = ll->pin + Ly.off_g; at.ld_gate = Ly.n_in;
+      at.pos_ptr = d_pos; at.scale = s.scale; at.B = B; at.L = L; at.H = H; at.Dk = Dk; at.Dv = s.kv_rank; at.M = m->M;
+      at.part_o = m->part_o; at.part_ml = m->part_ml;
+      at.nsplit = 1;
+      if (L == 1) {  // decode: the keys of a sequence spread over CTAs
+        const int ctas = B * ((H + 31) / 32);
+        at.nsplit = std::max(1, std::min(std::min(m->max_split, m->M / 64), (2 * 148) / std::max(1, ctas)));
+      }
+      LAUNCH(m, launch_latent_attn(at, m->bf16, m->stream));
+      if (at.nsplit > 1) m->launch_acc += 1;
+      // values out of the latent: ctx[r, h] = Wuv_h o[r, h]
+      HeadGemmArgs gv{};
+      gv.A = ll->o; gv.lda = H * s.kv_rank; gv.a_hs = s.kv_rank;
+      gv.W = Ly.w_uv; gv.w_hs = (int64_t)DV * s.kv_rank; gv.w_ks = 1; gv.w_js = s.kv_rank;
+      gv.C = m->ctx; gv.C16 = (bf16*)m->ctx16; gv.ldc = H * DV; gv.c_hs = DV;
+      gv.rows = ntok; gv.H = H; gv.J = DV; gv.K = s.kv_rank;
+      LAUNCH(m, launch_head_gemm(gv, m->bf16, m->stream));
+    } else if (s.mixer == L3_MIX_MINGRU) {
+      n_ctx = DK;
+      LAUNCH(m, launch_mingru_scan(ll->pin, Ly.n_in, Ly.off_b, Ly.off_v, Ly.off_g, Ly.in_bias, St.S, B, L, DK, m->ctx, (bf16*)m->ctx16, m->stream));
+    } else {
+      set_err(m, "mixer %d is not built for pre-norm layers", s.mixer);
+      return L3_EINVAL;
+    }
+    if ((rc = ll_linear(m, Ly.w_o, m->ctx, m->ctx16, 0, ntok, W, n_ctx, EPI_RESID, resid_into(m->x, W))) != L3_OK) return rc;
+    if (s.experts > 0) {
+      const int E = s.experts, ff = s.ff;
+      LAUNCH(m, launch_prenorm_shift(m->x, Ly.norm2, eps, nullptr, nullptr, B, L, W, hn, hn16, m->stream));
+      const bool few = ntok <= 8;  // few rows read only their chosen experts' weights; many share one GEMM over all experts
+      MoeRouteArgs ra{};
+      ra.h = hn; ra.router = Ly.router; ra.correction = Ly.correction; ra.D = W; ra.E = E; ra.I = s.identity; ra.top = s.top;
+      ra.groups = s.groups; ra.keep = s.groups_keep; ra.scale = s.router_scale;
+      ra.sel = ll->moe_sel; ra.w = ll->moe_w; ra.dense = few ? nullptr : ll->moe_dense; ra.idw = ll->moe_idw;
+      LAUNCH(m, launch_moe_route(ra, ntok, m->stream));
+      if (few) {
+        LAUNCH(m, launch_moe_rows(hn, Ly.w13, Ly.w2, m->bf16, ll->moe_sel, ll->moe_w, ll->moe_idw, ntok, W, E, ff, s.top, m->h, m->x, m->stream));
+        m->launch_acc += 1;
+      } else {
+        if ((rc = ll_linear(m, Ly.w13, hn, hn16, 0, ntok, E * ff, W, EPI_STORE, store_to(m->h, nullptr, E * ff))) != L3_OK) return rc;
+        LAUNCH(m, launch_moe_act_mask(m->h, ll->moe_dense, ntok, E, ff, (bf16*)m->h16, m->stream));
+        if ((rc = ll_linear(m, Ly.w2, m->h, m->h16, 0, ntok, W, E * ff, EPI_RESID, resid_into(m->x, W))) != L3_OK) return rc;
+        if (s.identity > 0) LAUNCH(m, launch_moe_identity(m->x, hn, ll->moe_idw, ntok, W, m->stream));
+      }
+    } else if (s.ff > 0) {
+      LAUNCH(m, launch_prenorm_shift(m->x, Ly.norm2, eps, nullptr, nullptr, B, L, W, hn, hn16, m->stream));
+      EpiArgs e = store_to(m->h, m->h16, s.ff);
+      e.act = ll->cfg.glu_act;
+      if ((rc = ll_linear(m, Ly.w13, hn, hn16, 0, ntok, 2 * s.ff, W, EPI_SWIGLU, e)) != L3_OK) return rc;
+      if ((rc = ll_linear(m, Ly.w2, m->h, m->h16, 0, ntok, W, s.ff, EPI_RESID, resid_into(m->x, W))) != L3_OK) return rc;
+    }
+    if (d_resid) CK(m, cudaMemcpyAsync(d_resid + (size_t)ri * ntok * W, m->x, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));
+  }
+  return L3_OK;
+}
+
 // ------------------------------------------------------------------------------ the layers of one chunk
 int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off, int B, int L, float* d_resid) {
   LayerList* ll = m->ll;
@@ -543,20 +829,28 @@ int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off,
   LLPending pd;
   // rows <= 8 never reach a tensor-core projection of the residual stream: no mirror needed
   if (x16 && !linear_rows_supported(ntok, W)) LAUNCH(m, launch_to_bf16(m->x, (int64_t)ntok * W, x16, m->stream));
-  for (int li = 0; li < (int)ll->layers.size(); ++li) {
+  if (ll->cfg.norm_input) return ll_enqueue_prenorm(m, B, L, d_resid);
+  for (int ri = 0; ri < (int)ll->runs.size(); ++ri) {
+    const int li = ll->runs[ri].layer;
     LLLayer& Ly = ll->layers[li];
+    LLState& St = ll->state[ri];
     const L3LayerSpec& s = Ly.spec;
     const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim, O = H * DV;
+    if (ll->runs[ri].pass >= 0) {  // a pass of the looped block starts: its step vector joins the stream
+      if ((rc = ll_settle(m, pd, ntok)) != L3_OK) return rc;
+      LAUNCH(m, launch_scale_add_rows(ll->xcur, 1.0f, ll->loop_step + (size_t)ll->runs[ri].pass * W, ntok, W, m->stream));
+      if (x16 && !linear_rows_supported(ntok, W)) LAUNCH(m, launch_to_bf16(ll->xcur, (int64_t)ntok * W, x16, m->stream));
+    }
     // every projection of the mixer's input in one GEMM
     if ((rc = ll_linear(m, Ly.w_in, ll->xcur, x16, 0, ntok, Ly.n_in, W, EPI_STORE, store_to(ll->pin, nullptr, Ly.n_in), &pd)) != L3_OK) return rc;
     if (s.mixer == L3_MIX_SOFTMAX) {
       QkNormArgs qa{};
       qa.proj = ll->pin; qa.ld = Ly.n_in; qa.k_off = Ly.off_k; qa.wq = Ly.q_norm; qa.wk = Ly.k_norm; qa.eps = eps;
-      qa.q_out = m->q; qa.cache_k = Ly.ck; qa.cache_v = Ly.cv; qa.pos_ptr = d_pos;
+      qa.q_out = m->q; qa.cache_k = St.ck; qa.cache_v = St.cv; qa.pos_ptr = d_pos;
       qa.L = L; qa.HN = H; qa.KVHN = G; qa.HD = DK; qa.M = m->M;
       LAUNCH(m, launch_qk_norm_cache(qa, ntok, m->bf16, m->stream));
       AttnArgs at{};
-      at.q = m->q; at.cache_k = Ly.ck; at.cache_v = Ly.cv; at.pos_ptr = d_pos;
+      at.q = m->q; at.cache_k = St.ck; at.cache_v = St.cv; at.pos_ptr = d_pos;
       at.B = B; at.L = L; at.HN = H; at.KVHN = G; at.HD = DK; at.M = m->M;
       at.part_o = m->part_o; at.part_ml = m->part_ml; at.counters = m->attn_cnt;
       at.out = m->ctx; at.out_bf16 = (bf16*)m->ctx16;
@@ -572,7 +866,7 @@ int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off,
       RecurArgs ra{};
       ra.mode = 0; ra.q = ll->pin + Ly.off_q; ra.k = ll->pin + Ly.off_k; ra.v = ll->pin + Ly.off_v;
       ra.ld_q = ra.ld_k = ra.ld_v = Ly.n_in; ra.act_in = m->bf16 ? 2 : 1; ra.head_decay = Ly.decay;
-      ra.state = Ly.S; ra.out = ll->o; ra.B = B; ra.L = L; ra.H = H; ra.rep = 1; ra.DK = DK; ra.DV = DV;
+      ra.state = St.S; ra.out = ll->o; ra.B = B; ra.L = L; ra.H = H; ra.rep = 1; ra.DK = DK; ra.DV = DV;
       ra.ws = ll->chunk_ws; ra.ws_floats = ll->chunk_ws_floats;
       LAUNCH(m, launch_recur(ra, m->stream));
       LAUNCH(m, launch_gated_rmsnorm(ll->o, ll->pin + Ly.off_g, Ly.n_in, Ly.mix_norm, O, O, eps, ntok, O, m->ctx, (bf16*)m->ctx16, m->stream));
@@ -584,14 +878,14 @@ int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off,
       if ((rc = ll_linear(m, Ly.w_g2, ll->pin + Ly.off_g1, nullptr, Ly.n_in, ntok, O, s.rank_gate, EPI_STORE, store_to(og, nullptr, O))) != L3_OK) return rc;
       DeltaPrepArgs pa{};
       pa.proj = ll->pin; pa.ld = Ly.n_in; pa.beta_off = Ly.off_b; pa.dt_in = dt; pa.ld_dt = nd;
-      pa.conv_w = Ly.conv_w; pa.conv_tail = Ly.conv_tail; pa.A_log = Ly.A_log; pa.dt_bias = Ly.dt_bias;
+      pa.conv_w = Ly.conv_w; pa.conv_tail = St.conv_tail; pa.A_log = Ly.A_log; pa.dt_bias = Ly.dt_bias;
       pa.q_out = m->q; pa.k_out = ll->rk; pa.v_out = ll->rv; pa.decay_out = ll->rg; pa.beta_out = ll->rbeta;
       pa.L = L; pa.H = H; pa.G = G; pa.DK = DK; pa.DV = DV; pa.taps = s.conv_taps;
       LAUNCH(m, launch_delta_prep(pa, ntok, m->stream));
-      if (s.conv_taps > 1) LAUNCH(m, launch_conv_tail(Ly.conv_tail, ll->pin, Ly.n_in, B, L, 2 * nq + O, s.conv_taps - 1, m->stream));
+      if (s.conv_taps > 1) LAUNCH(m, launch_conv_tail(St.conv_tail, ll->pin, Ly.n_in, B, L, 2 * nq + O, s.conv_taps - 1, m->stream));
       RecurArgs ra{};
       ra.mode = 1; ra.q = m->q; ra.k = ll->rk; ra.v = ll->rv; ra.ld_q = ra.ld_k = nq; ra.ld_v = O;
-      ra.g = ll->rg; ra.beta = ll->rbeta; ra.state = Ly.S; ra.out = ll->o;
+      ra.g = ll->rg; ra.beta = ll->rbeta; ra.state = St.S; ra.out = ll->o;
       ra.B = B; ra.L = L; ra.H = H; ra.rep = H / G; ra.DK = DK; ra.DV = DV;
       LAUNCH(m, launch_recur(ra, m->stream));
       LAUNCH(m, launch_gated_rmsnorm(ll->o, og, O, Ly.mix_norm, DV, DV, eps, ntok, O, m->ctx, (bf16*)m->ctx16, m->stream));
@@ -614,7 +908,7 @@ int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off,
     }
     if (d_resid) {
       if ((rc = ll_settle(m, pd, ntok)) != L3_OK) return rc;
-      CK(m, cudaMemcpyAsync(d_resid + (size_t)li * ntok * W, ll->xcur, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));
+      CK(m, cudaMemcpyAsync(d_resid + (size_t)ri * ntok * W, ll->xcur, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));
     }
   }
   return ll_settle(m, pd, ntok);  // the LM head reads ll->xcur

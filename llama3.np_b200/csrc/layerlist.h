@@ -29,15 +29,38 @@ struct LLLayer {
   float* conv_w = nullptr;    // gated delta: [2 kv_heads dim + heads vdim, taps]
   float *A_log = nullptr, *dt_bias = nullptr;
   float* decay = nullptr;     // decay-linear: [heads]
-  // ---- state per sequence slot
+  // latent attention: w_in = dq | dkv | g rows; q_norm / k_norm hold the two latent norms' weights
+  void* w_uq = nullptr;       // [heads * (dim + rot_dim), q_rank]
+  void* w_uk = nullptr;       // [heads * dim, kv_rank]
+  void* w_uv = nullptr;       // [heads * vdim, kv_rank]
+  float* inv_freq = nullptr;  // [rot_dims / 2] rot_base^(-2 i / rot_dims), rounded from double
+  float* in_bias = nullptr;   // minGRU: [2 dim] biases of the z and x segments of w_in
+  float* shift = nullptr;     // token shift: [width]
+  // mixture of experts: w13 = [experts * ff, width] up rows expert by expert, w2 = [width, experts * ff]
+  float* router = nullptr;      // [experts + identity, width] fp32
+  float* correction = nullptr;  // [experts + identity]
+};
+
+// What one layer RUN keeps per sequence slot (a layer inside the loop has one of these per pass).
+struct LLState {
   void *ck = nullptr, *cv = nullptr;  // softmax: [maxB, kv_heads, M, dim] of KVT (cv = keys as projected)
   float* S = nullptr;                 // recurrent: [maxB, heads, dim, vdim]
   float* conv_tail = nullptr;         // gated delta: [maxB, channels, taps - 1]
+  void* lat = nullptr;                // latent attention: [maxB, M, kv_rank + rot_dim] of KVT
+  float* hprev = nullptr;             // token shift: [maxB, width] the last token's normed mixer input
+};
+
+struct LLRun {
+  int layer = 0;
+  int pass = -1;       // >= 0: first layer of pass `pass` of the loop - the pass's step vector is added ahead of it
 };
 
 struct LayerList {
   L3StackConfig cfg{};
   std::vector<LLLayer> layers;
+  std::vector<LLRun> runs;       // execution order
+  std::vector<LLState> state;    // per run
+  float* loop_step = nullptr;    // [loop_times, width] fp32
   void* side_embed = nullptr;  // [vocab, n_layers * side_dim] of WT
   std::set<std::string> loaded;
   std::vector<int> slot_pos;   // next position of every sequence slot (host copy)
@@ -49,6 +72,11 @@ struct LayerList {
   float* x2 = nullptr;                     // second residual buffer, 8 rows (fused post-norm step of the GEMV path)
   float *xcur = nullptr, *xalt = nullptr;  // where the residual stream of the running step lives / the other buffer
   void* sg16 = nullptr;
+  // pre-norm / latent / mixture-of-experts workspace
+  float* qlat = nullptr;                   // [rows, heads, kv_rank + rot_dim] queries folded onto the latent
+  void* aux16 = nullptr;                   // bf16 mirror of aux (the query latent)
+  float *moe_w = nullptr, *moe_dense = nullptr, *moe_idw = nullptr;  // [rows, top] | [rows, experts] | [rows]
+  int32_t* moe_sel = nullptr;              // [rows, top]
   int max_in = 0, max_o = 0, max_ff = 0;
   int head_rows = 0;  // rows the LM head's buffers hold
 };

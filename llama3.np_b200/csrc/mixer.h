@@ -78,3 +78,82 @@ cudaError_t launch_recur_chunk(const RecurArgs& a, cudaStream_t s);
 
 // ---- attention for head sizes the tiled kernels do not take (attn_any.cu): same arguments, any HD
 cudaError_t launch_attn_any(const AttnArgs& a, bool kv_bf16, cudaStream_t s);
+
+// ---- pre-norm layers (prenorm_ops.cu)
+// out[r] = n(x[r]) + (prev - n(x[r])) * shift with n(v) = v / rms(v) * w (w: D weights) and prev = n(x[r - 1]) inside a
+// sequence, hprev[b] for its first token; the CTA of a sequence's first token then stores n(x[last row]) to hprev[b].
+// shift == null: plain norm.  out16 (may be null): bf16 mirror.
+cudaError_t launch_prenorm_shift(const float* x, const float* w, float eps, const float* shift, float* hprev, int B, int L,
+                                 int D, float* out, bf16* out16, cudaStream_t s);
+// x[r, i] = x[r, i] * mul + (vec ? vec[i] : 0)
+cudaError_t launch_scale_add_rows(float* x, float mul, const float* vec, int rows, int D, cudaStream_t s);
+
+// ---- latent attention (attn_latent.cu)
+struct LatentPrepArgs {
+  const float* proj;     // [rows, ld]: query latent at column 0 (q_rank), key latent at k_off (kv_rank), rotated key part behind it (rot_dim)
+  int ld, k_off;
+  const float *wq, *wk;  // norm weights [q_rank], [kv_rank]
+  float eps;
+  float* cq;             // [rows, q_rank] normed query latent (+ bf16 mirror, may be null)
+  bf16* cq16;
+  void* cache;           // [maxB, M, kv_rank + rot_dim] of KVT
+  const float* inv_freq; // [rot_dims / 2]
+  const int* pos_ptr;
+  int L, M, q_rank, kv_rank, rot_dim, rot_dims;
+};
+cudaError_t launch_latent_prep(const LatentPrepArgs& a, int rows, bool kv_bf16, cudaStream_t s);
+// rotated part of the queries: qlat[r, h, kv_rank + j] = rot(q[r, h, dim + j]) at the row's position
+cudaError_t launch_latent_q_rope(const float* q, float* qlat, const float* inv_freq, const int* pos_ptr, int rows, int L,
+                                 int H, int dim, int rot_dim, int rot_dims, int kv_rank, cudaStream_t s);
+// Batched per-head product  C[r, h, j] = sum_k A[r * lda + h * a_hs + k] * W[h * w_hs + k * w_ks + j * w_js]
+// for r < rows, h < H, j < J, k < K; C at c[r * ldc + h * c_hs + j] (+ bf16 mirror).  One of w_ks, w_js is 1.
+struct HeadGemmArgs {
+  const float* A; int lda, a_hs;
+  const void* W; int64_t w_hs; int w_ks, w_js;
+  float* C; bf16* C16; int ldc, c_hs;
+  int rows, H, J, K;
+};
+cudaError_t launch_head_gemm(const HeadGemmArgs& a, bool w_bf16, cudaStream_t s);
+struct LatentAttnArgs {
+  const float* q;        // [B * L, H, Dk] folded queries
+  const void* cache;     // [maxB, M, Dk] of KVT; a row's first Dv entries are also its value
+  float* out;            // [B * L, H, Dv]
+  const float* gate;     // head h of row r is multiplied by sigmoid(gate[r * ld_gate + h]) (null: none)
+  int ld_gate;
+  const int* pos_ptr;    // keys [0, *pos_ptr + t] are visible to token t
+  float scale;
+  int B, L, H, Dk, Dv, M;
+  int nsplit;            // > 1 (L == 1 only): every split writes (o, m, l) to part_o / part_ml, the combine kernel merges
+  float *part_o, *part_ml;
+};
+size_t latent_attn_smem(int Dk);
+bool latent_attn_supported(int Dk, int Dv);
+cudaError_t launch_latent_attn(const LatentAttnArgs& a, bool kv_bf16, cudaStream_t s);
+
+// ---- minGRU (mingru.cu): proj [rows, ld] = z | x | g logits of width n each at z_off, x_off, g_off; bias [2 n] (z, x)
+// S [maxB, n] is read and written; out[r, c] = S_t[c] * silu(g) (+ bf16 mirror)
+cudaError_t launch_mingru_scan(const float* proj, int ld, int z_off, int x_off, int g_off, const float* bias, float* S, int B,
+                               int L, int n, float* out, bf16* out16, cudaStream_t s);
+
+// ---- mixture of experts (moe.cu)
+struct MoeRouteArgs {
+  const float* h;        // [rows, D] router input
+  const float* router;   // [E + I, D] fp32
+  const float* correction;
+  int D, E, I, top, groups, keep;
+  float scale;
+  int32_t* sel;          // [rows, top] chosen slots, best first
+  float* w;              // [rows, top] their weights
+  float* dense;          // [rows, E] weight of every expert (0: not chosen); may be null
+  float* idw;            // [rows] summed weight of the chosen identity slots
+};
+cudaError_t launch_moe_route(const MoeRouteArgs& a, int rows, cudaStream_t s);
+// u[r, c] <- relu(u[r, c])^2 * dense[r, c / ff]  (+ bf16 mirror)
+cudaError_t launch_moe_act_mask(float* u, const float* dense, int rows, int E, int ff, bf16* out16, cudaStream_t s);
+// x[r, i] += idw[r] * h[r, i]
+cudaError_t launch_moe_identity(float* x, const float* h, const float* idw, int rows, int D, cudaStream_t s);
+// few rows: only the chosen experts' weights are read.  hid [rows * top, ff] = relu(up_e h)^2;
+// x[r] += sum_k w_k down_e hid_k + idw[r] h[r]
+cudaError_t launch_moe_rows(const float* h, const void* w_up, const void* w_down, bool w_bf16, const int32_t* sel,
+                            const float* w, const float* idw, int rows, int D, int E, int ff, int top, float* hid, float* x,
+                            cudaStream_t s);

@@ -1,0 +1,211 @@
+// Mixture-of-experts feed-forward of layer-list decoders (layerlist.cu).
+//
+//  * moe_route_kernel      one CTA per token: fp32 router logits over experts + identity slots, softmax, the choice
+//                          scores (score + correction), group limitation (only slots of the `keep` groups with the
+//                          largest best choice score stay eligible), the `top` largest choices (ties: lower slot),
+//                          weights = scale * score.  Emits the chosen slots and weights, the dense [rows, E] weight
+//                          table of the masked-dense path and the summed weight of the chosen identity slots.
+//  * moe_act_mask_kernel   masked-dense path (many rows): the up projection of ALL experts is one GEMM of the shared
+//                          projection kernels, this kernel turns it into relu(u)^2 * weight(row, expert) - zero for
+//                          experts the row did not choose - and one GEMM over K = experts * ff sums the experts.
+//  * moe_up_rows / moe_down_rows   few rows (decode): a warp per output reads only the chosen experts' rows.
+//  * moe_identity_kernel   x += (weight of the chosen identity slots) * h
+#include "common.cuh"
+#include "mixer.h"
+
+namespace {
+
+constexpr int MOE_MAX_SLOTS = 1024;
+
+__global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
+  __shared__ float s_score[MOE_MAX_SLOTS];   // logits, then softmax scores
+  __shared__ float s_choice[MOE_MAX_SLOTS];  // score + correction; -inf once taken or out of the kept groups
+  __shared__ float s_group[MOE_MAX_SLOTS];
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int n = a.E + a.I, D = a.D;
+  const float* h = a.h + (size_t)r * D;
+  for (int e = warp; e < n; e += nw) {
+    const float* wr = a.router + (size_t)e * D;
+    float acc = 0.f;
+    for (int i = lane; i < D; i += 32) acc = fmaf(wr[i], h[i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) s_score[e] = acc;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float mx = -INFINITY;
+  for (int e = lane; e < n; e += 32) mx = fmaxf(mx, s_score[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < n; e += 32) { const float p = expf(s_score[e] - mx); s_score[e] = p; sum += p; }
+  sum = warp_sum(sum);
+  const float inv = 1.0f / sum;
+  for (int e = lane; e < n; e += 32) {
+    const float sc = s_score[e] * inv;
+    s_score[e] = sc;
+    s_choice[e] = sc + a.correction[e];
+  }
+  __syncwarp();
+  const int per = n / a.groups;
+  if (a.groups > 1 && a.keep < a.groups) {
+    for (int g = lane; g < a.groups; g += 32) {
+      float best = -INFINITY;
+      for (int j = 0; j < per; ++j) best = fmaxf(best, s_choice[g * per + j]);
+      s_group[g] = best;
+    }
+    __syncwarp();
+    // the keep best groups get +inf as a mark, the others lose their slots
+    for (int k = 0; k < a.keep; ++k) {
+      float bv = -INFINITY; int bi = 0x7fffffff;
+      for (int g = lane; g < a.groups; g += 32) {
+        const float v = s_group[g];
+        if (v != INFINITY && (bi == 0x7fffffff || v > bv)) { bv = v; bi = g; }
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(L3_FULL, bv, o);
+        const int oi = __shfl_xor_sync(L3_FULL, bi, o);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+      }
+      if (lane == 0 && bi != 0x7fffffff) s_group[bi] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < n; e += 32)
+      if (s_group[e / per] != INFINITY) s_choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  if (a.dense)
+    for (int e = lane; e < a.E; e += 32) a.dense[(size_t)r * a.E + e] = 0.f;
+  __syncwarp();
+  float idw = 0.f;
+  for (int k = 0; k < a.top; ++k) {
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int e = lane; e < n; e += 32) {
+      const float v = s_choice[e];
+      if (v > bv) { bv = v; bi = e; }  // ascending e: the first of equal values stays
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(L3_FULL, bv, o);
+      const int oi = __shfl_xor_sync(L3_FULL, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) {
+      // fewer eligible slots than `top`: the surplus picks get weight 0 on slot 0
+      const bool ok = bi != 0x7fffffff;
+      const int e = ok ? bi : 0;
+      const float w = ok ? s_score[e] * a.scale : 0.f;
+      a.sel[(size_t)r * a.top + k] = e;
+      a.w[(size_t)r * a.top + k] = w;
+      if (ok) {
+        s_choice[e] = -INFINITY;
+        if (e >= a.E) idw += w;
+        else if (a.dense) a.dense[(size_t)r * a.E + e] = w;
+      }
+    }
+    __syncwarp();
+  }
+  if (lane == 0) a.idw[r] = idw;
+}
+
+__global__ void moe_act_mask_kernel(float* __restrict__ u, const float* __restrict__ dense, int64_t n, int E, int ff,
+                                    bf16* __restrict__ out16) {
+  pdl_launch();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t width = (int64_t)E * ff;
+  const int64_t r = i / width;
+  const int e = (int)((i - r * width) / ff);
+  const float w = dense[r * E + e];
+  const float v = fmaxf(u[i], 0.f);
+  const float o = w != 0.f ? v * v * w : 0.f;
+  u[i] = o;
+  if (out16) out16[i] = __float2bfloat16_rn(o);
+}
+
+__global__ void moe_identity_kernel(float* __restrict__ x, const float* __restrict__ h, const float* __restrict__ idw, int64_t n,
+                                    int D) {
+  pdl_launch();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float w = idw[i / D];
+  if (w != 0.f) x[i] = fmaf(w, h[i], x[i]);
+}
+
+template <typename WT>
+__device__ __forceinline__ float warp_dot(const WT* __restrict__ w, const float* __restrict__ v, int K, int lane) {
+  float acc = 0.f;
+  for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(w[k]), v[k], acc);
+  return warp_sum(acc);
+}
+
+// grid (ceil(ff / 8), rows * top): hid[pair, j] = relu(up_e[j] . h[row])^2
+template <typename WT>
+__global__ void __launch_bounds__(256) moe_up_rows_kernel(const float* __restrict__ h, const WT* __restrict__ w_up,
+                                                          const int32_t* __restrict__ sel, int D, int E, int ff, int top,
+                                                          float* __restrict__ hid) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pair = blockIdx.y, j = blockIdx.x * 8 + warp;
+  const int e = sel[pair];
+  if (j >= ff || e >= E) return;
+  const float d = warp_dot(w_up + ((size_t)e * ff + j) * D, h + (size_t)(pair / top) * D, D, lane);
+  if (lane == 0) { const float v = fmaxf(d, 0.f); hid[(size_t)pair * ff + j] = v * v; }
+}
+
+// grid (ceil(D / 8), rows): x[row, i] += sum_k w_k down_e[i] . hid[pair_k] + idw[row] h[row, i]
+template <typename WT>
+__global__ void __launch_bounds__(256) moe_down_rows_kernel(const float* __restrict__ h, const WT* __restrict__ w_down,
+                                                            const int32_t* __restrict__ sel, const float* __restrict__ w,
+                                                            const float* __restrict__ idw, int D, int E, int ff, int top,
+                                                            const float* __restrict__ hid, float* __restrict__ x) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.y, i = blockIdx.x * 8 + warp;
+  if (i >= D) return;
+  float acc = 0.f;
+  for (int k = 0; k < top; ++k) {
+    const int pair = row * top + k, e = sel[pair];
+    if (e >= E) continue;
+    acc = fmaf(w[pair], warp_dot(w_down + (size_t)i * E * ff + (size_t)e * ff, hid + (size_t)pair * ff, ff, lane), acc);
+  }
+  if (lane == 0) x[(size_t)row * D + i] += acc + idw[row] * h[(size_t)row * D + i];
+}
+
+}  // namespace
+
+cudaError_t launch_moe_route(const MoeRouteArgs& a, int rows, cudaStream_t s) {
+  if (a.E + a.I > MOE_MAX_SLOTS || a.groups < 1 || (a.E + a.I) % a.groups) return cudaErrorInvalidValue;
+  return launch_k(moe_route_kernel, dim3(rows), dim3(128), 0, s, a);
+}
+
+cudaError_t launch_moe_act_mask(float* u, const float* dense, int rows, int E, int ff, bf16* out16, cudaStream_t s) {
+  const int64_t n = (int64_t)rows * E * ff;
+  return launch_k(moe_act_mask_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, u, dense, n, E, ff, out16);
+}
+
+cudaError_t launch_moe_identity(float* x, const float* h, const float* idw, int rows, int D, cudaStream_t s) {
+  const int64_t n = (int64_t)rows * D;
+  return launch_k(moe_identity_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, x, h, idw, n, D);
+}
+
+cudaError_t launch_moe_rows(const float* h, const void* w_up, const void* w_down, bool w_bf16, const int32_t* sel,
+                            const float* w, const float* idw, int rows, int D, int E, int ff, int top, float* hid, float* x,
+                            cudaStream_t s) {
+  cudaError_t e;
+  const dim3 gu((ff + 7) / 8, rows * top), gd((D + 7) / 8, rows);
+  if (w_bf16) {
+    e = launch_k(moe_up_rows_kernel<bf16>, gu, dim3(256), 0, s, h, (const bf16*)w_up, sel, D, E, ff, top, hid);
+    if (e != cudaSuccess) return e;
+    return launch_k(moe_down_rows_kernel<bf16>, gd, dim3(256), 0, s, h, (const bf16*)w_down, sel, w, idw, D, E, ff, top,
+                    (const float*)hid, x);
+  }
+  e = launch_k(moe_up_rows_kernel<float>, gu, dim3(256), 0, s, h, (const float*)w_up, sel, D, E, ff, top, hid);
+  if (e != cudaSuccess) return e;
+  return launch_k(moe_down_rows_kernel<float>, gd, dim3(256), 0, s, h, (const float*)w_down, sel, w, idw, D, E, ff, top,
+                  (const float*)hid, x);
+}

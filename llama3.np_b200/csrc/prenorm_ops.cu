@@ -1,0 +1,124 @@
+// Row kernels of pre-norm layer-list decoders (layerlist.cu): everything fp32.
+//
+//  * prenorm_shift_kernel   h = x / rms(x) * w, optionally mixed with the previous token's h (token shift):
+//                           out = h + (h_prev - h) * shift.  The previous token's h is the un-shifted one; for the
+//                           first token of a call it comes from the slot's state, which the same CTA then replaces
+//                           by the h of the call's last token (so no other CTA reads or writes that state row).
+//  * scale_add_rows_kernel  x = x * mul + vec   (embedding multiplier, the per-pass vector of a looped block)
+//  * mingru_scan_kernel     the element-wise gated recurrence over the tokens of a call, one thread per channel
+#include "common.cuh"
+#include "mixer.h"
+
+namespace {
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < nw; ++w) t += red[w];
+  return t;
+}
+
+__device__ __forceinline__ float row_rinv(const float* __restrict__ row, int D, float eps, float* red) {
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) { const float v = row[i]; ss = fmaf(v, v, ss); }
+  return 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps);
+}
+
+__global__ void __launch_bounds__(256) prenorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
+                                                            const float* __restrict__ shift, float* __restrict__ hprev, int L,
+                                                            int D, float* __restrict__ out, bf16* __restrict__ out16) {
+  __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
+  const size_t r = blockIdx.x;
+  const int b = (int)(r / L), t = (int)(r - (size_t)b * L);
+  const float* xr = x + r * D;
+  const float rc = row_rinv(xr, D, eps, red);
+  if (!shift) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      const float h = xr[i] * rc * w[i];
+      out[r * D + i] = h;
+      if (out16) out16[r * D + i] = __float2bfloat16_rn(h);
+    }
+    return;
+  }
+  const float* xp = xr - D;  // previous token of the same sequence (t > 0)
+  const float rp = t > 0 ? row_rinv(xp, D, eps, red) : 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float h = xr[i] * rc * w[i];
+    const float prev = t > 0 ? xp[i] * rp * w[i] : hprev[(size_t)b * D + i];
+    const float v = h + (prev - h) * shift[i];
+    out[r * D + i] = v;
+    if (out16) out16[r * D + i] = __float2bfloat16_rn(v);
+  }
+  if (t == 0) {  // this CTA alone touches hprev[b]: read above, replaced here
+    const float* xl = xr + (size_t)(L - 1) * D;
+    const float rl = L > 1 ? row_rinv(xl, D, eps, red) : rc;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) hprev[(size_t)b * D + i] = xl[i] * rl * w[i];
+  }
+}
+
+__global__ void scale_add_rows_kernel(float* __restrict__ x, float mul, const float* __restrict__ vec, int64_t n, int D) {
+  pdl_launch();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  x[i] = fmaf(x[i], mul, vec ? vec[i % D] : 0.f);
+}
+
+// One thread per (sequence, channel); the loads of the next token are issued before this token's chain of
+// dependent operations so that the chain, not the memory latency, sets the pace.
+__global__ void __launch_bounds__(128) mingru_scan_kernel(const float* __restrict__ proj, int ld, int z_off, int x_off, int g_off,
+                                                          const float* __restrict__ bias, float* __restrict__ S, int L, int n,
+                                                          float* __restrict__ out, bf16* __restrict__ out16) {
+  pdl_launch();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (c >= n) return;
+  const float bz = bias[c], bx = bias[n + c];
+  float s = S[(size_t)b * n + c];
+  const float* p = proj + (size_t)b * L * ld;
+  float zl = p[z_off + c], ul = p[x_off + c], gl = p[g_off + c];
+  for (int t = 0; t < L; ++t) {
+    const float zc = zl, uc = ul, gc = gl;
+    if (t + 1 < L) {
+      const float* pn = p + (size_t)(t + 1) * ld;
+      zl = pn[z_off + c]; ul = pn[x_off + c]; gl = pn[g_off + c];
+    }
+    const float z = sigmoid_f(zc + bz);
+    const float u = uc + bx;
+    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+    s = (1.0f - z) * s + z * cand;
+    const float o = s * (gc * sigmoid_f(gc));
+    const size_t oi = ((size_t)b * L + t) * n + c;
+    out[oi] = o;
+    if (out16) out16[oi] = __float2bfloat16_rn(o);
+  }
+  S[(size_t)b * n + c] = s;
+}
+
+int row_threads(int D) { return D >= 1024 ? 256 : D >= 256 ? 128 : 64; }
+
+}  // namespace
+
+cudaError_t launch_prenorm_shift(const float* x, const float* w, float eps, const float* shift, float* hprev, int B, int L,
+                                 int D, float* out, bf16* out16, cudaStream_t s) {
+  return launch_k(prenorm_shift_kernel, dim3(B * L), dim3(row_threads(D)), 0, s, x, w, eps, shift, hprev, L, D, out, out16);
+}
+
+cudaError_t launch_scale_add_rows(float* x, float mul, const float* vec, int rows, int D, cudaStream_t s) {
+  const int64_t n = (int64_t)rows * D;
+  return launch_k(scale_add_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, x, mul, vec, n, D);
+}
+
+cudaError_t launch_mingru_scan(const float* proj, int ld, int z_off, int x_off, int g_off, const float* bias, float* S, int B,
+                               int L, int n, float* out, bf16* out16, cudaStream_t s) {
+  return launch_k(mingru_scan_kernel, dim3((n + 127) / 128, B), dim3(128), 0, s, proj, ld, z_off, x_off, g_off, bias, S, L, n, out,
+                  out16);
+}

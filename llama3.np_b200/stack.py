@@ -11,19 +11,20 @@ from __future__ import annotations
 
 import ctypes as C
 from dataclasses import dataclass, field
-from typing import List, Mapping, Optional, Sequence
+from typing import List, Mapping, Optional, Sequence, Tuple
 
 import numpy as np
 
 from . import _cabi
 
 SOFTMAX, DECAY_LINEAR, GATED_DELTA = _cabi.MIX_SOFTMAX, _cabi.MIX_DECAY_LINEAR, _cabi.MIX_GATED_DELTA
+LATENT, MINGRU = _cabi.MIX_LATENT, _cabi.MIX_MINGRU
 _DTYPES = {"float32": _cabi.DTYPE_F32, "fp32": _cabi.DTYPE_F32, "bfloat16": _cabi.DTYPE_BF16, "bf16": _cabi.DTYPE_BF16}
 
 
 @dataclass
 class LayerSpec:
-    mixer: int                    # SOFTMAX | DECAY_LINEAR | GATED_DELTA
+    mixer: int                    # SOFTMAX | DECAY_LINEAR | GATED_DELTA | LATENT | MINGRU
     heads: int
     dim: int
     vdim: int
@@ -34,6 +35,17 @@ class LayerSpec:
     ff: int = 0                   # 0: no feed-forward in this layer
     scale: float = 0.0            # SOFTMAX: multiplier of q . k
     decay: Sequence[float] = ()   # DECAY_LINEAR: one per head
+    q_rank: int = 0               # LATENT: width of the query latent
+    kv_rank: int = 0              # LATENT: width of the cached key / value latent
+    rot_dim: int = 0              # LATENT: rotated query / key size per head (dim is the un-rotated size)
+    rot_dims: int = 0             # LATENT: leading entries of the rotated part that turn
+    rot_base: float = 10000.0
+    experts: int = 0              # > 0: the feed-forward is a mixture of experts of width ff each
+    top: int = 0
+    identity: int = 0             # router slots behind the experts that return their input
+    groups: int = 1
+    groups_keep: int = 1
+    router_scale: float = 1.0
 
 
 @dataclass
@@ -46,6 +58,11 @@ class StackConfig:
     norm_one_plus: bool = True
     glu_act: str = "gelu_tanh"    # "silu" | "gelu_tanh"
     side_dim: int = 0
+    norm_input: bool = False      # pre-norm layers: x += sublayer(norm(x))
+    norm_scalar: bool = False     # every norm has one weight
+    token_shift: bool = False     # the mixer reads its input mixed with the previous token's
+    embed_scale: float = 1.0
+    loop: Optional[Tuple[int, int, int]] = None   # (start, stop, times): layers [start, stop) run `times` times
     max_seq_len: int = 256
     max_batch_size: int = 1
     dtype: str = "float32"
@@ -70,13 +87,22 @@ class StackDecoder:
                 raise ValueError(f"layer {i}: {len(l.decay)} decays for {l.heads} heads")
             specs[i] = _cabi.L3LayerSpec(mixer=l.mixer, heads=l.heads, kv_heads=l.kv_heads or l.heads, dim=l.dim, vdim=l.vdim,
                                          conv_taps=l.conv_taps, rank_decay=l.rank_decay, rank_gate=l.rank_gate, ff=l.ff,
-                                         scale=l.scale, decay=C.cast(dec, C.POINTER(C.c_float)) if len(l.decay) else None)
+                                         scale=l.scale, decay=C.cast(dec, C.POINTER(C.c_float)) if len(l.decay) else None,
+                                         q_rank=l.q_rank, kv_rank=l.kv_rank, rot_dim=l.rot_dim, rot_dims=l.rot_dims,
+                                         rot_base=float(l.rot_base), experts=l.experts, top=l.top, identity=l.identity,
+                                         groups=l.groups, groups_keep=l.groups_keep, router_scale=float(l.router_scale))
         c = _cabi.L3StackConfig(width=cfg.width, vocab=cfg.vocab, n_layers=len(cfg.layers), max_seq_len=cfg.max_seq_len,
                                 max_batch_size=cfg.max_batch_size, dtype=_DTYPES[cfg.dtype], device=device, flags=flags,
                                 norm_eps=cfg.norm_eps, residual_mult=cfg.residual_mult, norm_one_plus=int(cfg.norm_one_plus),
                                 glu_act=_cabi.GLU_GELU_TANH if cfg.glu_act == "gelu_tanh" else _cabi.GLU_SILU,
-                                side_dim=cfg.side_dim)
+                                side_dim=cfg.side_dim, norm_input=int(cfg.norm_input), norm_scalar=int(cfg.norm_scalar),
+                                token_shift=int(cfg.token_shift), embed_scale=float(cfg.embed_scale),
+                                loop_start=cfg.loop[0] if cfg.loop else 0, loop_stop=cfg.loop[1] if cfg.loop else 0,
+                                loop_times=cfg.loop[2] if cfg.loop else 0)
         _cabi.check(self._lib.l3_create_stack(C.byref(c), specs, C.byref(self._h)))
+        n = C.c_int()
+        _cabi.check(self._lib.l3_stack_runs(self._h, C.byref(n)), self._h)
+        self.n_runs = n.value  # executions of a layer per token: a layer inside the loop counts once per pass
 
     # ---------------------------------------------------------------- lifetime / weights
     def close(self):
@@ -96,6 +122,8 @@ class StackDecoder:
         try:
             for name in tensors.keys():
                 w = np.ascontiguousarray(tensors[name], dtype=np.float32)
+                if w.ndim == 0:  # a single number travels as a vector of one
+                    w = w.reshape(1)
                 shape = (C.c_int64 * max(1, w.ndim))(*w.shape)
                 _cabi.check(self._lib.l3_load_tensor(self._h, name.encode(), _cabi.f32p(w), shape, w.ndim), self._h)
             self.finalize()
@@ -142,12 +170,12 @@ class StackDecoder:
 
     def forward_rows(self, input_ids, start_pos: int, rows, want_residual: bool = False):
         """As `forward`, returning the logits `[len(rows), vocab]` of the chosen rows (`b * L + t`); with
-        `want_residual` also the residual stream after every layer, `[n_layers, B * L, width]`."""
+        `want_residual` also the residual stream after every layer run, `[n_runs, B * L, width]`."""
         ids = self._ids(input_ids)
         B, L = ids.shape
         rows = np.ascontiguousarray(np.asarray(rows, dtype=np.int32).reshape(-1))
         logits = np.empty((len(rows), self.cfg.vocab), dtype=np.float32)
-        resid = np.empty((len(self.cfg.layers), B * L, self.cfg.width), dtype=np.float32) if want_residual else None
+        resid = np.empty((self.n_runs, B * L, self.cfg.width), dtype=np.float32) if want_residual else None
         _cabi.check(self._lib.l3_forward_rows(self._h, _cabi.i32p(ids), B, L, int(start_pos),
                                               _cabi.i32p(rows) if len(rows) else None, len(rows),
                                               _cabi.f32p(logits) if len(rows) else None,
@@ -207,9 +235,27 @@ class StackDecoder:
         return out
 
     # ---------------------------------------------------------------- state inspection / measurement
+    def run_layer(self, run: int) -> int:
+        """Index of the layer that layer run `run` executes."""
+        n = len(self.cfg.layers)
+        if not self.cfg.loop:
+            return run
+        start, stop, times = self.cfg.loop
+        span = stop - start
+        if run < start:
+            return run
+        if run < start + span * times:
+            return start + (run - start) % span
+        return run - span * (times - 1)
+
     def read_state(self, layer: int, slot: int = 0):
-        """(S [heads, dim, vdim], conv tail [channels, taps - 1] or None) of a recurrent layer's slot."""
-        l = self.cfg.layers[layer]
+        """(S [heads, dim, vdim], conv tail [channels, taps - 1] or None) of a recurrent layer run's slot; for a
+        latent-attention run S is its cache `[max_seq_len, kv_rank + rot_dim]`.  `layer` counts layer runs."""
+        l = self.cfg.layers[self.run_layer(layer)]
+        if l.mixer == LATENT:
+            S = np.empty((self.cfg.max_seq_len, l.kv_rank + l.rot_dim), dtype=np.float32)
+            _cabi.check(self._lib.l3_read_state(self._h, layer, slot, _cabi.f32p(S), None), self._h)
+            return S, None
         S = np.empty((l.heads, l.dim, l.vdim), dtype=np.float32)
         tail = None
         if l.mixer == GATED_DELTA:
@@ -221,7 +267,7 @@ class StackDecoder:
 
     def read_cache(self, layer: int):
         """(keys, values) `[max_batch, max_seq_len, kv_heads, dim]` float32 of a softmax layer."""
-        l = self.cfg.layers[layer]
+        l = self.cfg.layers[self.run_layer(layer)]
         shape = (self.cfg.max_batch_size, self.cfg.max_seq_len, l.kv_heads or l.heads, l.dim)
         k = np.empty(shape, dtype=np.float32)
         v = np.empty(shape, dtype=np.float32)
