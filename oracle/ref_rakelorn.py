@@ -84,11 +84,13 @@ def latent_attention_step(h, pos, P, mc, eps, st):
     Wuk = P["mix.uk"].reshape(H, dn, rank)
     Wuv = P["mix.uv"].reshape(H, dv, rank)
     out = np.zeros((H, dv))
+    st["p"] = []                   # the last token's attention weights, head by head (tests look at them)
     for j in range(H):
         qr = rotate_pairs(q[j, dn:], pos, rot["dims"], rot["base"])
         K = C @ Wuk[j].T           # [T, dn]
         V = C @ Wuv[j].T           # [T, dv]
         p = softmax((K @ q[j, :dn] + KR @ qr) * mc["scale"])
+        st["p"].append(p)
         out[j] = gate[j] * (p @ V)
     return P["mix.o"] @ out.reshape(-1)
 
