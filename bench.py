@@ -656,9 +656,43 @@ def risalix_layer_params(cfg):
     return tot
 
 
+# ------------------------------------------------------------------------------ --arch rakelorn
+# Six layers (latent attention, latent attention, minGRU, twice), every one with a mixture of 16 relu^2 experts
+# (4 chosen, 2 identity slots, 2 groups of which 1 is kept); layers 1-2 run twice (8 layer runs per token).
+def rakelorn_bench_config(width, vocab=32000):
+    heads = max(1, width // 128)
+    mlp = {"kind": "moe", "expert": {"ff": width // 2},
+           "router": {"experts": 16, "top": 4, "identity": 2, "scale": 2.5, "groups": {"count": 2, "keep": 1}}}
+    lat = {"type": "latent_attention",
+           "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 4, "kv_rank": 512,
+                     "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}, "mlp": mlp}
+    gru = {"type": "mingru", "mixer": {"width": 3 * width // 2}, "mlp": mlp}
+    return {"architecture": "Rakelorn", "layers": [lat, lat, gru, lat, lat, gru], "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "loop": {"start": 1, "stop": 3, "times": 2}, "vocab": vocab, "width": width}
+
+
+def rakelorn_layer_params(cfg):
+    """(parameters held, parameters a token reads over all its layer runs: chosen experts only, looped layers per pass)"""
+    W, held, read = cfg["width"], 0, 0
+    lp = cfg.get("loop") or {"start": 0, "stop": 0, "times": 1}
+    for i, lc in enumerate(cfg["layers"]):
+        mc, rc, ff = lc["mixer"], lc["mlp"]["router"], lc["mlp"]["expert"]["ff"]
+        if lc["type"] == "latent_attention":
+            H, dn, dr, dv = mc["heads"], mc["dim"], mc["rot_dim"], mc["vdim"]
+            mix = W * (mc["q_rank"] + mc["kv_rank"] + dr + H) + mc["q_rank"] * H * (dn + dr) + mc["kv_rank"] * H * (dn + dv) + W * H * dv
+        else:
+            mix = 4 * W * mc["width"]
+        router = (rc["experts"] + rc["identity"]) * W
+        held += mix + router + rc["experts"] * 2 * W * ff
+        runs = lp["times"] if lp["start"] <= i < lp["stop"] else 1
+        read += runs * (mix + router + rc["top"] * 2 * W * ff)
+    return held, read
+
+
 def run_arch_compare(a):
     import llama3_np_b200  # noqa: F401
     from llama3_np_b200 import Llama, ModelArgs, _cabi
+    from llama3_np_b200.rakelorn import Rakelorn
     from llama3_np_b200.risalix import Risalix
     lib = _cabi.lib()
     hbm, tflops, how = peaks()
@@ -677,7 +711,8 @@ def run_arch_compare(a):
         _cabi.check(lib.l3_timer_stop(m._h, C.byref(ms)), m._h)
         return ms.value / iters
 
-    def measure(m, vocab, layer_params, is_stack):
+    def measure(m, vocab, layer_params, is_stack, flop_params=None):
+        flop_params = flop_params or layer_params
         rng = np.random.default_rng(0)
         rec = {}
         ids = rng.integers(3, vocab, (1, L_pre)).astype(np.int32)
@@ -685,7 +720,7 @@ def run_arch_compare(a):
         fwd = (lambda: m.forward(ids, 0)) if is_stack else (lambda: m.forward_f32(ids, 0))
         ms = timed_ms(m, fwd, a.steps)
         rec["prefill"] = {"tokens": L_pre, "ms": ms, "tokens_per_s": L_pre / ms * 1e3,
-                          "tensor_frac_of_" + how: 2.0 * layer_params * L_pre / (ms / 1e3) / 1e12 / tflops}
+                          "tensor_frac_of_" + how: 2.0 * flop_params * L_pre / (ms / 1e3) / 1e12 / tflops}
         for B in (1, 8):
             p = rng.integers(3, vocab, (B, 8)).astype(np.int32)
             gen = (lambda: m.generate_all(p, n_dec)) if is_stack else (lambda: m.generate_all(p, 8 + n_dec))
@@ -699,15 +734,21 @@ def run_arch_compare(a):
     out = []
     for name in a.arch_sizes.split(","):
         W = ARCH_SIZES[name]
-        cfg = risalix_bench_config(W)
-        rp = risalix_layer_params(cfg)
+        if a.arch == "rakelorn":
+            cfg = rakelorn_bench_config(W)
+            rp, rp_read = rakelorn_layer_params(cfg)
+        else:
+            cfg = risalix_bench_config(W)
+            rp = rp_read = risalix_layer_params(cfg)
         heads, kv, ff = W // 128, max(1, W // 512), 4 * W
         lp1 = W * (heads * 128 + 2 * kv * 128) + W * heads * 128 + 3 * W * ff
         nl = max(1, round(rp / lp1))
         clock = ClockSampler(0)
         clock.start()
-        r = Risalix(cfg, None, dtype=dtype, max_seq_len=M, max_batch_size=8, random_seed=1)
-        rec_r = measure(r, cfg["vocab"], rp + cfg["vocab"] * W, True)
+        r = (Rakelorn if a.arch == "rakelorn" else Risalix)(cfg, None, dtype=dtype, max_seq_len=M, max_batch_size=8, random_seed=1)
+        # the decode leg streams what a token reads (chosen experts, looped layers once per pass), the prefill leg's
+        # useful work is the same count per token
+        rec_r = measure(r, cfg["vocab"], rp_read + cfg["vocab"] * W, True)
         r.close()
         la = ModelArgs(dim=W, n_layers=nl, n_heads=heads, n_kv_heads=kv, vocab_size=cfg["vocab"], max_seq_len=M + 8,
                        max_batch_size=8, dtype=dtype)
@@ -715,9 +756,9 @@ def run_arch_compare(a):
         rec_l = measure(l, cfg["vocab"], nl * lp1 + cfg["vocab"] * W, False)
         l.close()
         clk = clock.stop()
-        out.append({"size": name, "width": W, "risalix": {"layers": len(cfg["layers"]), "params_in_layers": rp, **rec_r},
+        out.append({"size": name, "width": W, a.arch: {"layers": len(cfg["layers"]), "params_in_layers": rp, "params_read_per_token": rp_read, **rec_r},
                     "llama": {"layers": nl, "params_in_layers": nl * lp1, **rec_l}, "clocks": clk})
-    print(json.dumps({"metric": "prefill / decode tokens/s, layer-list decoder (Risalix) beside Llama at equal width and size",
+    print(json.dumps({"metric": f"prefill / decode tokens/s, layer-list decoder ({a.arch.capitalize()}) beside Llama at equal width and size",
                       "dtype": a.dtype, "data": "synthetic", "steps": a.steps, "warmup": a.warmup, "peak_source": how,
                       "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops}, "sizes": out}))
 
@@ -733,7 +774,7 @@ def main():
     ap.add_argument("--total-len", type=int, default=256, help="profiling only: shorter generate")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="profiling only: skip the CPU legs")
     ap.add_argument("--no-extra", action="store_true", help="headline only: skip the `extra` / `tp` sub-records")
-    ap.add_argument("--arch", default="", choices=["", "risalix"],
+    ap.add_argument("--arch", default="", choices=["", "risalix", "rakelorn"],
                     help="instead of the headline: prefill / decode throughput of this decoder family beside Llama at equal size")
     ap.add_argument("--arch-sizes", default="w1024,w2048", help="comma list of " + ",".join(ARCH_SIZES))
     ap.add_argument("--arch-prefill", type=int, default=2048)

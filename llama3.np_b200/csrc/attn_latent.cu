@@ -110,21 +110,31 @@ __global__ void __launch_bounds__(256) head_gemm_kernel(HeadGemmArgs a) {
   const float* A = a.A + (size_t)h * a.a_hs;
   const WT* W = (const WT*)a.W + (size_t)h * a.w_hs;
   float acc[4][4] = {};
-  for (int k0 = 0; k0 < a.K; k0 += HG_BK) {
-    // A tile: consecutive threads read consecutive k of one row
-    for (int e = tid; e < HG_BM * HG_BK; e += 256) {
+  // a thread moves 4 elements of each tile; the next tile's global loads are issued ahead of this tile's products
+  float ra[4], rb[4];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = tid + u * 256;
       const int k = e & (HG_BK - 1), rr = e >> 4;
       const int r = r0 + rr, kk = k0 + k;
-      As[k][rr] = (r < a.rows && kk < a.K) ? A[(size_t)r * a.lda + kk] : 0.f;
+      ra[u] = (r < a.rows && kk < a.K) ? A[(size_t)r * a.lda + kk] : 0.f;
+      int kb, jj;
+      if (a.w_js == 1) { jj = e & (HG_BN - 1); kb = e >> 6; } else { kb = e & (HG_BK - 1); jj = e >> 4; }
+      const int j = j0 + jj, kw = k0 + kb;
+      rb[u] = (j < a.J && kw < a.K) ? to_f32(W[(size_t)kw * a.w_ks + (size_t)j * a.w_js]) : 0.f;
     }
-    // W tile: consecutive threads follow the unit stride
-    for (int e = tid; e < HG_BN * HG_BK; e += 256) {
-      int k, jj;
-      if (a.w_js == 1) { jj = e & (HG_BN - 1); k = e >> 6; } else { k = e & (HG_BK - 1); jj = e >> 4; }
-      const int j = j0 + jj, kk = k0 + k;
-      Bs[k][jj] = (j < a.J && kk < a.K) ? to_f32(W[(size_t)kk * a.w_ks + (size_t)j * a.w_js]) : 0.f;
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < a.K; k0 += HG_BK) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = tid + u * 256;
+      As[e & (HG_BK - 1)][e >> 4] = ra[u];
+      if (a.w_js == 1) Bs[e >> 6][e & (HG_BN - 1)] = rb[u]; else Bs[e & (HG_BK - 1)][e >> 4] = rb[u];
     }
     __syncthreads();
+    if (k0 + HG_BK < a.K) fetch(k0 + HG_BK);
 #pragma unroll
     for (int k = 0; k < HG_BK; ++k) {
       const float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
@@ -153,7 +163,7 @@ __global__ void __launch_bounds__(256) head_gemm_kernel(HeadGemmArgs a) {
 }
 
 // ---------------------------------------------------------------- attention over the latent cache
-constexpr int LA_ROWS = 32, LA_KT = 32, LA_RW = 4, LA_WARPS = 8;
+constexpr int LA_ROWS = 32, LA_KT = 32, LA_RW = 4, LA_WARPS = 8, LA_PF = 10;
 
 __host__ __device__ inline int la_kstride(int Dk) {
   // 16-byte loads by 8 lanes at a time want an odd stride in 16-byte units; scalar loads an odd stride in words
@@ -185,9 +195,21 @@ __global__ void __launch_bounds__(256) attn_latent_kernel(LatentAttnArgs a) {
     k_end = min(k_end, k_begin + per);
   }
   const float* qg = a.q + ((size_t)b * nrow + row0) * Dk;
-  for (int e = threadIdx.x; e < LA_ROWS * Dk; e += blockDim.x) {
-    const int rr = e / Dk, d = e - rr * Dk;
-    Qs[rr * QS + d] = rr < rows_here ? qg[e] * a.scale : 0.f;
+  if (Dk % 4 == 0) {
+    const int nv = LA_ROWS * Dk / 4;
+#pragma unroll 4
+    for (int v = threadIdx.x; v < nv; v += 256) {
+      const int rr = (v * 4) / Dk, d = v * 4 - rr * Dk;
+      float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (rr < rows_here) q4 = *reinterpret_cast<const float4*>(qg + (size_t)v * 4);
+      *reinterpret_cast<float4*>(Qs + rr * QS + d) = make_float4(q4.x * a.scale, q4.y * a.scale, q4.z * a.scale, q4.w * a.scale);
+    }
+  } else {
+#pragma unroll 8
+    for (int e = threadIdx.x; e < LA_ROWS * Dk; e += 256) {
+      const int rr = e / Dk, d = e - rr * Dk;
+      Qs[rr * QS + d] = rr < rows_here ? qg[e] * a.scale : 0.f;
+    }
   }
   // this warp's rows and their last visible key
   int lim[LA_RW];
@@ -206,15 +228,55 @@ __global__ void __launch_bounds__(256) attn_latent_kernel(LatentAttnArgs a) {
   const KVT* cb = (const KVT*)a.cache + (size_t)b * a.M * Dk;
   const bool vec4 = (Dk % 4) == 0;
   float* Pw = Ps + warp * LA_KT * LA_RW;
+  // A tile of cache rows is one contiguous block.  With rows that are a whole number of 16-byte vectors every thread
+  // keeps up to LA_PF vectors of the NEXT tile in registers: their loads are in flight while this tile is used.
+  constexpr int VEC = 16 / (int)sizeof(KVT);
+  const bool kvec = (Dk % VEC) == 0 && vec4;
+  uint4 pf[LA_PF];
+  auto issue = [&](int k0n) {
+    const int nvec = min(LA_KT, k_end - k0n) * Dk / VEC;
+    const KVT* srcn = cb + (size_t)k0n * Dk;
+#pragma unroll
+    for (int u = 0; u < LA_PF; ++u) {
+      const int v = threadIdx.x + u * 256;
+      if (v < nvec) pf[u] = ldg_stream16(srcn + (size_t)v * VEC);
+    }
+  };
+  auto put = [&](const uint4& r, int v) {  // vector v of the tile: VEC entries of one row
+    const int e = v * VEC, j = e / Dk, d = e - j * Dk;
+    float f[VEC];
+    Vec16<KVT>::unpack(r, f);
+#pragma unroll
+    for (int x = 0; x < VEC; x += 4) *reinterpret_cast<float4*>(Ks + j * KS + d + x) = make_float4(f[x], f[x + 1], f[x + 2], f[x + 3]);
+  };
+  if (kvec && k_begin < k_end) issue(k_begin);
   for (int k0 = k_begin; k0 < k_end; k0 += LA_KT) {
     const int nk = min(LA_KT, k_end - k0);
     __syncthreads();  // the previous tile is consumed (first pass: Qs is complete)
     const KVT* src = cb + (size_t)k0 * Dk;
-    for (int e = threadIdx.x; e < nk * Dk; e += blockDim.x) {
-      const int j = e / Dk, d = e - j * Dk;
-      Ks[j * KS + d] = to_f32(src[e]);
+    if (kvec) {
+      const int nvec = nk * Dk / VEC;
+#pragma unroll
+      for (int u = 0; u < LA_PF; ++u) {
+        const int v = threadIdx.x + u * 256;
+        if (v < nvec) put(pf[u], v);
+      }
+      for (int v0 = threadIdx.x + LA_PF * 256; v0 < nvec; v0 += 4 * 256) {  // rows too long for the registers
+        uint4 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (v0 + u * 256 < nvec) r[u] = ldg_stream16(src + (size_t)(v0 + u * 256) * VEC);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (v0 + u * 256 < nvec) put(r[u], v0 + u * 256);
+      }
+    } else {
+#pragma unroll 8
+      for (int e = threadIdx.x; e < nk * Dk; e += 256) {
+        const int j = e / Dk, d = e - j * Dk;
+        Ks[j * KS + d] = to_f32(src[e]);
+      }
     }
     __syncthreads();
+    if (kvec && k0 + LA_KT < k_end) issue(k0 + LA_KT);
     // scores: lane = key
     float s[LA_RW] = {0.f, 0.f, 0.f, 0.f};
     if (lane < nk) {

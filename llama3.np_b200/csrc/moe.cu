@@ -17,7 +17,31 @@ namespace {
 
 constexpr int MOE_MAX_SLOTS = 1024;
 
-__global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
+// w . v over K entries by one warp; rows of whole 16-byte vectors (aligned base) take vector loads, four in flight
+template <typename WT>
+__device__ __forceinline__ float warp_dot(const WT* __restrict__ w, const float* __restrict__ v, int K, int lane) {
+  constexpr int VEC = Vec16<WT>::N;
+  float acc = 0.f;
+  if (K % VEC == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)v & 15) == 0) {
+#pragma unroll 4
+    for (int k = lane * VEC; k < K; k += 32 * VEC) {
+      float f[VEC];
+      Vec16<WT>::load(w + k, f);
+#pragma unroll
+      for (int x = 0; x < VEC; x += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(v + k + x);
+        acc = fmaf(f[x], a.x, acc); acc = fmaf(f[x + 1], a.y, acc); acc = fmaf(f[x + 2], a.z, acc); acc = fmaf(f[x + 3], a.w, acc);
+      }
+    }
+  } else {
+#pragma unroll 4
+    for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(w[k]), v[k], acc);
+  }
+  return warp_sum(acc);
+}
+
+
+__global__ void __launch_bounds__(256) moe_route_kernel(MoeRouteArgs a) {
   __shared__ float s_score[MOE_MAX_SLOTS];   // logits, then softmax scores
   __shared__ float s_choice[MOE_MAX_SLOTS];  // score + correction; -inf once taken or out of the kept groups
   __shared__ float s_group[MOE_MAX_SLOTS];
@@ -27,10 +51,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
   const int n = a.E + a.I, D = a.D;
   const float* h = a.h + (size_t)r * D;
   for (int e = warp; e < n; e += nw) {
-    const float* wr = a.router + (size_t)e * D;
-    float acc = 0.f;
-    for (int i = lane; i < D; i += 32) acc = fmaf(wr[i], h[i], acc);
-    acc = warp_sum(acc);
+    const float acc = warp_dot(a.router + (size_t)e * D, h, D, lane);
     if (lane == 0) s_score[e] = acc;
   }
   __syncthreads();
@@ -134,13 +155,6 @@ __global__ void moe_identity_kernel(float* __restrict__ x, const float* __restri
   if (w != 0.f) x[i] = fmaf(w, h[i], x[i]);
 }
 
-template <typename WT>
-__device__ __forceinline__ float warp_dot(const WT* __restrict__ w, const float* __restrict__ v, int K, int lane) {
-  float acc = 0.f;
-  for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(w[k]), v[k], acc);
-  return warp_sum(acc);
-}
-
 // grid (ceil(ff / 8), rows * top): hid[pair, j] = relu(up_e[j] . h[row])^2
 template <typename WT>
 __global__ void __launch_bounds__(256) moe_up_rows_kernel(const float* __restrict__ h, const WT* __restrict__ w_up,
@@ -180,7 +194,7 @@ __global__ void __launch_bounds__(256) moe_down_rows_kernel(const float* __restr
 
 cudaError_t launch_moe_route(const MoeRouteArgs& a, int rows, cudaStream_t s) {
   if (a.E + a.I > MOE_MAX_SLOTS || a.groups < 1 || (a.E + a.I) % a.groups) return cudaErrorInvalidValue;
-  return launch_k(moe_route_kernel, dim3(rows), dim3(128), 0, s, a);
+  return launch_k(moe_route_kernel, dim3(rows), dim3(256), 0, s, a);
 }
 
 cudaError_t launch_moe_act_mask(float* u, const float* dense, int rows, int E, int ff, bf16* out16, cudaStream_t s) {

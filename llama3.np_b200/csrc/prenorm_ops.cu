@@ -72,8 +72,9 @@ __global__ void scale_add_rows_kernel(float* __restrict__ x, float mul, const fl
   x[i] = fmaf(x[i], mul, vec ? vec[i % D] : 0.f);
 }
 
-// One thread per (sequence, channel); the loads of the next token are issued before this token's chain of
-// dependent operations so that the chain, not the memory latency, sets the pace.
+// One thread per (sequence, channel); the loads of the next GRU_AHEAD tokens are in flight while a token's chain of
+// dependent operations runs, so that the chain, not the memory latency, sets the pace.
+constexpr int GRU_AHEAD = 8;
 __global__ void __launch_bounds__(128) mingru_scan_kernel(const float* __restrict__ proj, int ld, int z_off, int x_off, int g_off,
                                                           const float* __restrict__ bias, float* __restrict__ S, int L, int n,
                                                           float* __restrict__ out, bf16* __restrict__ out16) {
@@ -84,21 +85,30 @@ __global__ void __launch_bounds__(128) mingru_scan_kernel(const float* __restric
   const float bz = bias[c], bx = bias[n + c];
   float s = S[(size_t)b * n + c];
   const float* p = proj + (size_t)b * L * ld;
-  float zl = p[z_off + c], ul = p[x_off + c], gl = p[g_off + c];
-  for (int t = 0; t < L; ++t) {
-    const float zc = zl, uc = ul, gc = gl;
-    if (t + 1 < L) {
-      const float* pn = p + (size_t)(t + 1) * ld;
-      zl = pn[z_off + c]; ul = pn[x_off + c]; gl = pn[g_off + c];
+  // a ring of GRU_AHEAD tokens in registers: the loads of token t + GRU_AHEAD are issued while token t is computed
+  float zq[GRU_AHEAD], uq[GRU_AHEAD], gq[GRU_AHEAD];
+#pragma unroll
+  for (int i = 0; i < GRU_AHEAD; ++i)
+    if (i < L) { const float* pn = p + (size_t)i * ld; zq[i] = pn[z_off + c]; uq[i] = pn[x_off + c]; gq[i] = pn[g_off + c]; }
+  for (int t0 = 0; t0 < L; t0 += GRU_AHEAD) {
+#pragma unroll
+    for (int i = 0; i < GRU_AHEAD; ++i) {
+      const int t = t0 + i;
+      if (t >= L) break;
+      const float zc = zq[i], uc = uq[i], gc = gq[i];
+      if (t + GRU_AHEAD < L) {
+        const float* pn = p + (size_t)(t + GRU_AHEAD) * ld;
+        zq[i] = pn[z_off + c]; uq[i] = pn[x_off + c]; gq[i] = pn[g_off + c];
+      }
+      const float z = sigmoid_f(zc + bz);
+      const float u = uc + bx;
+      const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+      s = (1.0f - z) * s + z * cand;
+      const float o = s * (gc * sigmoid_f(gc));
+      const size_t oi = ((size_t)b * L + t) * n + c;
+      out[oi] = o;
+      if (out16) out16[oi] = __float2bfloat16_rn(o);
     }
-    const float z = sigmoid_f(zc + bz);
-    const float u = uc + bx;
-    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-    s = (1.0f - z) * s + z * cand;
-    const float o = s * (gc * sigmoid_f(gc));
-    const size_t oi = ((size_t)b * L + t) * n + c;
-    out[oi] = o;
-    if (out16) out16[oi] = __float2bfloat16_rn(o);
   }
   S[(size_t)b * n + c] = s;
 }
