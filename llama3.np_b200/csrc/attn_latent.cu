@@ -6,7 +6,8 @@
 //
 //  * latent_prep_kernel        norms of the two latents, rotation of k_r, cache append (one CTA per token)
 //  * latent_q_rope_kernel      rotated query part into the folded query
-//  * head_gemm_kernel          batched per-head product (Wuk_j^T q_c and Wuv_j ctx): 64 x 64 FFMA tiles, 4 x 4 per thread
+//  * head_gemm_kernel          batched per-head product (Wuk_j^T q_c and Wuv_j ctx): 64 x 64 FFMA tiles, 4 x 4 per thread;
+//                              head_gemv_kernel for up to 8 rows (decode)
 //  * attn_latent_kernel        flash-style exact attention: a CTA holds 32 (token, head) query rows in shared memory
 //                              and walks the visible cache rows 32 at a time; a lane scores one key for its warp's
 //                              four query rows, then the lanes own output columns.  Scores, weights and sums fp32.
@@ -351,24 +352,61 @@ __global__ void __launch_bounds__(256) attn_latent_kernel(LatentAttnArgs a) {
 }
 
 __global__ void __launch_bounds__(128) attn_latent_combine_kernel(LatentAttnArgs a) {
+  __shared__ float wsplit[64];
   pdl_launch();
   pdl_wait();
   const size_t row = blockIdx.x;
   const float* ml = a.part_ml + row * a.nsplit * 2;
   float mx = -INFINITY;
   for (int s = 0; s < a.nsplit; ++s) mx = fmaxf(mx, ml[2 * s]);
+  if (threadIdx.x < a.nsplit) wsplit[threadIdx.x] = ml[2 * threadIdx.x] == -INFINITY ? 0.f : expf(ml[2 * threadIdx.x] - mx);
+  __syncthreads();
   float l = 0.f;
-  for (int s = 0; s < a.nsplit; ++s) l += ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - mx) * ml[2 * s + 1];
+  for (int s = 0; s < a.nsplit; ++s) l = fmaf(wsplit[s], ml[2 * s + 1], l);
   const size_t tok = row / a.H;
   const int head = (int)(row - tok * a.H);
   const float g = a.gate ? 1.0f / (1.0f + expf(-a.gate[tok * a.ld_gate + head])) : 1.0f;
   const float inv = g / l;
+  const float* po = a.part_o + row * a.nsplit * a.Dv;
   for (int d = threadIdx.x; d < a.Dv; d += blockDim.x) {
     float o = 0.f;
-    for (int s = 0; s < a.nsplit; ++s)
-      if (ml[2 * s] != -INFINITY) o = fmaf(expf(ml[2 * s] - mx), a.part_o[(row * a.nsplit + s) * a.Dv + d], o);
+#pragma unroll 8
+    for (int s = 0; s < a.nsplit; ++s) o = fmaf(wsplit[s], po[(size_t)s * a.Dv + d], o);
     a.out[row * a.Dv + d] = o * inv;
   }
+}
+
+// Few rows (decode): the per-head product as matrix-vector products that stream the head's weights once.
+// w_ks == 1 (an output's weights are contiguous): a warp per output; w_js == 1: a thread per output, the k loop unrolled.
+template <typename WT>
+__global__ void __launch_bounds__(256) head_gemv_kernel(HeadGemmArgs a) {
+  pdl_launch();
+  pdl_wait();
+  const int h = blockIdx.y, r = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* A = a.A + (size_t)r * a.lda + (size_t)h * a.a_hs;
+  const WT* W = (const WT*)a.W + (size_t)h * a.w_hs;
+  float v;
+  int j;
+  if (a.w_ks == 1) {
+    j = blockIdx.x * 8 + warp;
+    if (j >= a.J) return;
+    const WT* wr = W + (size_t)j * a.w_js;
+    float acc = 0.f;
+#pragma unroll 4
+    for (int k = lane; k < a.K; k += 32) acc = fmaf(to_f32(wr[k]), A[k], acc);
+    v = warp_sum(acc);
+    if (lane != 0) return;
+  } else {
+    j = blockIdx.x * 256 + threadIdx.x;
+    if (j >= a.J) return;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int k = 0; k < a.K; ++k) acc = fmaf(to_f32(W[(size_t)k * a.w_ks + j]), A[k], acc);
+    v = acc;
+  }
+  const size_t o = (size_t)r * a.ldc + (size_t)h * a.c_hs + j;
+  a.C[o] = v;
+  if (a.C16) a.C16[o] = __float2bfloat16_rn(v);
 }
 
 template <typename KVT>
@@ -418,6 +456,11 @@ cudaError_t launch_latent_q_rope(const float* q, float* qlat, const float* inv_f
 }
 
 cudaError_t launch_head_gemm(const HeadGemmArgs& a, bool w_bf16, cudaStream_t s) {
+  if (a.rows <= 8) {
+    const dim3 g(a.w_ks == 1 ? (a.J + 7) / 8 : (a.J + 255) / 256, a.H, a.rows);
+    if (w_bf16) return launch_k(head_gemv_kernel<bf16>, g, dim3(256), 0, s, a);
+    return launch_k(head_gemv_kernel<float>, g, dim3(256), 0, s, a);
+  }
   const dim3 grid((a.rows + HG_BM - 1) / HG_BM, (a.J + HG_BN - 1) / HG_BN, a.H);
   if (w_bf16) return launch_k(head_gemm_kernel<bf16>, grid, dim3(256), 0, s, a);
   return launch_k(head_gemm_kernel<float>, grid, dim3(256), 0, s, a);

@@ -13,7 +13,23 @@
 //   then the output projection and the post-norm residual kernel, which also emits the bf16 mirror of the new
 //   residual rows for the next tensor-core projection.
 //
-// Precision: norms, gates, decays, scores, softmax, recurrent state and the residual sum are fp32 in both
+//
+// Pre-norm stacks (L3StackConfig::norm_input):  x += mixer(shift(norm1(x)));  x += ff(norm2(x)), the norms with one
+// weight or one per coordinate, the mixer's input optionally mixed with the previous token's (token shift, one saved
+// row per sequence slot and layer run), the output projections adding into x in their epilogue.  Two mixers:
+//
+//   latent        fused dq|dkv|g projection -> norms of both latents, rotation of the shared key part, append of the
+//                 [latent | rotated part] row to the run's cache -> query up-projection -> queries folded onto the
+//                 latent per head (Wuk^T q) -> attention over the cache rows themselves, all heads of a token against
+//                 the same rows (attn_latent.cu), gate per head -> values out of the latent per head (Wuv o)
+//   minGRU        fused z|x|g projection -> element-wise gated recurrence (prenorm_ops.cu)
+//   and a feed-forward that is a mixture of experts (moe.cu): fp32 router -> few rows: only the chosen experts' weights
+//   are read; many rows: ONE up-projection over all experts, relu^2 times the routing weight (zero where not chosen),
+//   ONE down-projection whose K runs over all experts and so sums them.
+// A block of layers can run several times per token (loop_*): the execution order is a list of layer RUNS, every run
+// with its own cache / state (LLState); the pass's step vector is added ahead of the block's first layer.
+//
+// Precision: norms, gates, decays, scores, softmax, router, recurrent state and the residual sum are fp32 in both
 // modes; bf16 mode rounds only GEMM operands (weights, and activations on the tensor-core path) and the KV cache.
 #include "layerlist.h"
 

@@ -131,8 +131,8 @@ bool latent_attn_supported(int Dk, int Dv);
 cudaError_t launch_latent_attn(const LatentAttnArgs& a, bool kv_bf16, cudaStream_t s);
 
 // ---- minGRU (mingru.cu): proj [rows, ld] = z | x | g logits of width n each at z_off, x_off, g_off; bias [2 n] (z, x)
-// S [maxB, n] is read and written; out[r, c] = S_t[c] * silu(g) (+ bf16 mirror)
-cudaError_t launch_mingru_scan(const float* proj, int ld, int z_off, int x_off, int g_off, const float* bias, float* S, int B,
+// S [maxB, n] is read and written; out[r, c] = S_t[c] * silu(g) (+ bf16 mirror).  Prompts overwrite proj with the gates.
+cudaError_t launch_mingru_scan(float* proj, int ld, int z_off, int x_off, int g_off, const float* bias, float* S, int B,
                                int L, int n, float* out, bf16* out16, cudaStream_t s);
 
 // ---- mixture of experts (moe.cu)

@@ -5,7 +5,8 @@
 //                           first token of a call it comes from the slot's state, which the same CTA then replaces
 //                           by the h of the call's last token (so no other CTA reads or writes that state row).
 //  * scale_add_rows_kernel  x = x * mul + vec   (embedding multiplier, the per-pass vector of a looped block)
-//  * mingru_scan_kernel     the element-wise gated recurrence over the tokens of a call, one thread per channel
+//  * mingru_scan_kernel     the element-wise gated recurrence over the tokens of a call, one thread per channel;
+//                           prompts run as mingru_gates_kernel (all gates at once) + mingru_chain_kernel (S <- a S + b)
 #include "common.cuh"
 #include "mixer.h"
 
@@ -113,6 +114,66 @@ __global__ void __launch_bounds__(128) mingru_scan_kernel(const float* __restric
   S[(size_t)b * n + c] = s;
 }
 
+// Prompts: the gates of all tokens at once (every (token, channel) on its own), in place over the projection:
+// z column <- 1 - z, x column <- z * candidate, g column <- silu(g) ...
+__global__ void mingru_gates_kernel(float* __restrict__ proj, int ld, int z_off, int x_off, int g_off,
+                                    const float* __restrict__ bias, int64_t rows, int n) {
+  pdl_launch();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * n) return;
+  const int64_t r = i / n;
+  const int c = (int)(i - r * n);
+  float* p = proj + r * ld;
+  const float z = sigmoid_f(p[z_off + c] + bias[c]);
+  const float u = p[x_off + c] + bias[n + c];
+  const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+  const float g = p[g_off + c];
+  p[z_off + c] = 1.0f - z;
+  p[x_off + c] = z * cand;
+  p[g_off + c] = g * sigmoid_f(g);
+}
+
+// ... and then the chain alone: S <- a S + b per token, a thread per (sequence, channel), GRU_AHEAD tokens of loads in flight
+__global__ void __launch_bounds__(128) mingru_chain_kernel(const float* __restrict__ proj, int ld, int z_off, int x_off, int g_off,
+                                                           float* __restrict__ S, int L, int n, float* __restrict__ out,
+                                                           bf16* __restrict__ out16) {
+  pdl_launch();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (c >= n) return;
+  float s = S[(size_t)b * n + c];
+  const float* p = proj + (size_t)b * L * ld + c;
+  float aq[GRU_AHEAD], bq[GRU_AHEAD], gq[GRU_AHEAD];
+  const int Lfull = L / GRU_AHEAD * GRU_AHEAD;
+  if (Lfull) {
+#pragma unroll
+    for (int i = 0; i < GRU_AHEAD; ++i) { const float* pn = p + (size_t)i * ld; aq[i] = pn[z_off]; bq[i] = pn[x_off]; gq[i] = pn[g_off]; }
+  }
+  for (int t0 = 0; t0 < Lfull; t0 += GRU_AHEAD) {
+    const bool more = t0 + GRU_AHEAD < Lfull;
+#pragma unroll
+    for (int i = 0; i < GRU_AHEAD; ++i) {
+      const float a = aq[i], bb = bq[i], g = gq[i];
+      if (more) { const float* pn = p + (size_t)(t0 + GRU_AHEAD + i) * ld; aq[i] = pn[z_off]; bq[i] = pn[x_off]; gq[i] = pn[g_off]; }
+      s = a * s + bb;
+      const float o = s * g;
+      const size_t oi = ((size_t)b * L + t0 + i) * n + c;
+      out[oi] = o;
+      if (out16) out16[oi] = __float2bfloat16_rn(o);
+    }
+  }
+  for (int t = Lfull; t < L; ++t) {
+    const float* pn = p + (size_t)t * ld;
+    s = pn[z_off] * s + pn[x_off];
+    const float o = s * pn[g_off];
+    const size_t oi = ((size_t)b * L + t) * n + c;
+    out[oi] = o;
+    if (out16) out16[oi] = __float2bfloat16_rn(o);
+  }
+  S[(size_t)b * n + c] = s;
+}
+
 int row_threads(int D) { return D >= 1024 ? 256 : D >= 256 ? 128 : 64; }
 
 }  // namespace
@@ -127,8 +188,16 @@ cudaError_t launch_scale_add_rows(float* x, float mul, const float* vec, int row
   return launch_k(scale_add_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, x, mul, vec, n, D);
 }
 
-cudaError_t launch_mingru_scan(const float* proj, int ld, int z_off, int x_off, int g_off, const float* bias, float* S, int B,
+cudaError_t launch_mingru_scan(float* proj, int ld, int z_off, int x_off, int g_off, const float* bias, float* S, int B,
                                int L, int n, float* out, bf16* out16, cudaStream_t s) {
+  if (L > 16) {  // a prompt: gates in parallel, then the bare chain
+    const int64_t tot = (int64_t)B * L * n;
+    cudaError_t e = launch_k(mingru_gates_kernel, dim3((unsigned)((tot + 255) / 256)), dim3(256), 0, s, proj, ld, z_off, x_off, g_off,
+                             bias, (int64_t)B * L, n);
+    if (e != cudaSuccess) return e;
+    return launch_k(mingru_chain_kernel, dim3((n + 127) / 128, B), dim3(128), 0, s, (const float*)proj, ld, z_off, x_off, g_off, S, L,
+                    n, out, out16);
+  }
   return launch_k(mingru_scan_kernel, dim3((n + 127) / 128, B), dim3(128), 0, s, proj, ld, z_off, x_off, g_off, bias, S, L, n, out,
                   out16);
 }
