@@ -657,18 +657,18 @@ def risalix_layer_params(cfg):
 
 
 # ------------------------------------------------------------------------------ --arch rakelorn
-# Six layers (latent attention, latent attention, minGRU, twice), every one with a mixture of 16 relu^2 experts
-# (4 chosen, 2 identity slots, 2 groups of which 1 is kept); layers 1-2 run twice (8 layer runs per token).
+# Six layers (latent attention, minGRU, latent, latent, minGRU, latent), every one with a mixture of 16 relu^2 experts
+# (4 chosen, 4 identity slots, 4 groups of which 2 are kept); layers 3-4 run twice (8 layer runs per token).
 def rakelorn_bench_config(width, vocab=32000):
     heads = max(1, width // 128)
     mlp = {"kind": "moe", "expert": {"ff": width // 2},
-           "router": {"experts": 16, "top": 4, "identity": 2, "scale": 2.5, "groups": {"count": 2, "keep": 1}}}
+           "router": {"experts": 16, "top": 4, "identity": 4, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
     lat = {"type": "latent_attention",
            "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 4, "kv_rank": 512,
                      "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}, "mlp": mlp}
     gru = {"type": "mingru", "mixer": {"width": 3 * width // 2}, "mlp": mlp}
-    return {"architecture": "Rakelorn", "layers": [lat, lat, gru, lat, lat, gru], "norm": {"eps": 1e-5},
-            "embedding": {"scale": 1.0}, "loop": {"start": 1, "stop": 3, "times": 2}, "vocab": vocab, "width": width}
+    return {"architecture": "Rakelorn", "layers": [lat, gru, lat, lat, gru, lat], "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "loop": {"start": 3, "stop": 5, "times": 2}, "vocab": vocab, "width": width}
 
 
 def rakelorn_layer_params(cfg):
