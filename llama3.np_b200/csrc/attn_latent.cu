@@ -424,7 +424,7 @@ cudaError_t launch_la(const LatentAttnArgs& a, cudaStream_t s) {
     }                                                                                                                     \
     return launch_k(attn_latent_kernel<KVT, N>, grid, dim3(256), smem, s, a);                                             \
   }
-  LA_CASE(1) LA_CASE(2) LA_CASE(4) LA_CASE(8) LA_CASE(16)
+  LA_CASE(1) LA_CASE(2) LA_CASE(4) LA_CASE(8) LA_CASE(16) LA_CASE(32)
 #undef LA_CASE
   return cudaErrorInvalidValue;
 }
@@ -435,7 +435,7 @@ size_t latent_attn_smem(int Dk) {
   return ((size_t)LA_ROWS * ((Dk + 3) & ~3) + (size_t)LA_KT * la_kstride(Dk) + LA_WARPS * LA_KT * LA_RW) * sizeof(float);
 }
 
-bool latent_attn_supported(int Dk, int Dv) { return Dv >= 1 && Dv <= Dk && Dv <= 512 && latent_attn_smem(Dk) <= 220 * 1024; }
+bool latent_attn_supported(int Dk, int Dv) { return Dv >= 1 && Dv <= Dk && Dv <= 1024 && latent_attn_smem(Dk) <= 220 * 1024; }
 
 cudaError_t launch_latent_attn(const LatentAttnArgs& a, bool kv_bf16, cudaStream_t s) {
   cudaError_t e = kv_bf16 ? launch_la<bf16>(a, s) : launch_la<float>(a, s);

@@ -322,6 +322,7 @@ ODD = {
     "row_not_4": config([latent(heads=5, dim=6, rot_dim=6, vdim=6, q_rank=10, kv_rank=13, scale=0.5)], width=40, vocab=25),
     "many_heads": config([latent(heads=35, dim=4, rot_dim=4, vdim=2, q_rank=12, kv_rank=8, scale=0.5)], width=24, vocab=25),
     "wide_values": config([latent(heads=2, dim=8, rot_dim=8, vdim=72, q_rank=12, kv_rank=136, scale=0.3, mlp=moe(experts=2, top=1, ff=80, identity=0))], width=48, vocab=31),
+    "long_latent": config([latent(heads=2, dim=8, rot_dim=16, vdim=8, q_rank=8, kv_rank=600, scale=0.3)], width=32, vocab=31),
     "no_feed_forward": config([gru(width=16), latent(heads=2), gru(width=128)], width=16, vocab=20, loop=(1, 2, 2)),
 }
 
